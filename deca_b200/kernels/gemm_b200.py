@@ -1,0 +1,151 @@
+"""16-bit tensor-core GEMM configs for B200 and their binding to the native library.
+
+Mirrors the module-level surface of the reference's src/kernels/gemm_tir.py -- ``GemmConfig``
+(:42-76), ``smem_bytes`` (:79-89), ``check_config`` (:101-120), ``make_gemm_tc`` (:123),
+``build_gemm_tc`` (:392-398), ``build_gemm_tc_to_file`` (:401-407) -- with the tile space
+of the tcgen05 kernel in csrc/gemm_f16.cu instead of the mma.sync one: there are no warp
+tiles (one thread issues the MMAs, the accumulator lives in tensor memory), the CTA tile is
+the MMA tile (BM = 128 rows per CTA, BN <= 256 columns), ``cta_group = 2`` pairs two CTAs on
+a 256-row tile, ``stages`` counts TMA pipeline slots and ``acc_bufs`` tensor-memory
+accumulators (2 lets the epilogue of one tile overlap the main loop of the next).
+"""
+
+from __future__ import annotations
+
+from dataclasses import asdict, dataclass
+
+from .module import KernelModule, KernelSpec, _check_tensor, current_stream_ptr
+
+MAX_DYN_SMEM = 232448  # 227 KB opt-in per CTA
+TMEM_COLUMNS = 512
+SMEM_RESERVED = 2048  # barriers, tensor-memory base slot, alignment slack
+GEMM_DTYPES = ("float16", "bfloat16")
+
+
+@dataclass(frozen=True)
+class GemmConfig:
+    BM: int = 128  # tile rows per CTA (the tcgen05 M)
+    BN: int = 256  # tile columns (the tcgen05 N)
+    BK: int = 64  # K depth of one pipeline stage (one 128-byte swizzle row of fp16)
+    stages: int = 4  # TMA -> MMA shared-memory ring depth
+    raster: int = 8  # tile rows per rasterization group (1: plain row-major order)
+    epi_smem: bool = True  # stage C through shared memory and write it with TMA stores
+    cta_group: int = 1  # 2: two CTAs of a cluster share one 256-row MMA tile
+    acc_bufs: int = 2  # tensor-memory accumulator buffers
+
+    @property
+    def threads(self) -> int:
+        return 192  # TMA warp + MMA warp + 4 epilogue warps
+
+    @property
+    def tile_m(self) -> int:
+        return self.BM * self.cta_group
+
+    def as_dict(self):
+        return asdict(self)
+
+    def __str__(self):
+        return (
+            f"{self.tile_m}x{self.BN}x{self.BK},cta={self.cta_group},stages={self.stages},"
+            f"raster={self.raster},epi_smem={int(self.epi_smem)},acc={self.acc_bufs}"
+        )
+
+
+def pipeline_smem_bytes(cfg: GemmConfig) -> int:
+    # per CTA: its A rows and (BN / cta_group) of the B columns per stage
+    return cfg.stages * (cfg.BM * cfg.BK + cfg.BK * cfg.BN // cfg.cta_group) * 2
+
+
+def epilogue_smem_bytes(cfg: GemmConfig) -> int:
+    # two 128 x 64 staging panels (double buffered TMA stores)
+    return 2 * cfg.BM * 64 * 2 if cfg.epi_smem else 0
+
+
+def smem_bytes(cfg: GemmConfig) -> int:
+    return pipeline_smem_bytes(cfg) + epilogue_smem_bytes(cfg) + SMEM_RESERVED
+
+
+def tmem_columns(cfg: GemmConfig) -> int:
+    cols = cfg.acc_bufs * cfg.BN
+    p = 32
+    while p < cols:
+        p *= 2
+    return p
+
+
+def check_config(cfg: GemmConfig, M: int, N: int, K: int, max_smem: int = MAX_DYN_SMEM) -> None:
+    assert cfg.BM == 128 and cfg.BK == 64
+    assert cfg.BN in (64, 128, 256)
+    assert cfg.cta_group in (1, 2) and cfg.acc_bufs in (1, 2)
+    assert 2 <= cfg.stages <= 8
+    assert cfg.raster >= 1
+    assert tmem_columns(cfg) <= TMEM_COLUMNS
+    assert smem_bytes(cfg) <= max_smem
+    assert M >= 1 and N >= 8 and K >= 8
+    # TMA needs 16-byte row pitches; partial tiles are zero-filled / clipped by TMA
+    assert N % 8 == 0 and K % 8 == 0
+
+
+def default_config(M: int, N: int, K: int) -> GemmConfig:
+    """A reasonable config without tuning: the widest tile that still gives every SM a tile."""
+    bn = 256
+    while bn > 64 and (N % bn != 0 and N < bn or -(-M // 128) * -(-N // bn) < 148):
+        bn //= 2
+    gm = -(-M // 128)
+    raster = 8
+    while raster > 1 and gm < raster:
+        raster //= 2
+    stages = 4 if bn == 256 else 6
+    return GemmConfig(BN=bn, stages=stages, raster=raster)
+
+
+def make_gemm_tc(M: int, N: int, K: int, cfg: GemmConfig, dtype: str = "float16") -> KernelSpec:
+    check_config(cfg, M, N, K)
+    assert dtype in GEMM_DTYPES
+    return KernelSpec("gemm", (M, N, K), dtype, cfg.as_dict())
+
+
+def build_gemm_tc(mod: KernelSpec, target=None, dump_dir=None) -> KernelModule:
+    return KernelModule(mod)
+
+
+def build_gemm_tc_to_file(shape, cfg: GemmConfig, arch: str, path: str, dtype: str = "float16") -> str:
+    """Writes the kernel spec to ``path`` (safe in a worker process without a CUDA context)."""
+    M, N, K = shape
+    return make_gemm_tc(M, N, K, cfg, dtype).export_library(path)
+
+
+def native_cfg(cfg: GemmConfig):
+    from .. import native
+
+    return native.GemmCfg(cfg.BM, cfg.BN, cfg.BK, cfg.stages, cfg.raster, int(cfg.epi_smem), cfg.cta_group,
+                          cfg.acc_bufs)
+
+
+def bind(spec: KernelSpec):
+    """Returns main(a, b, c) launching deca_gemm16 on torch's current stream."""
+    import ctypes
+
+    import torch
+
+    from .. import native
+
+    L = native.lib()
+    M, N, K = spec.shape
+    cfg = GemmConfig(**spec.config)
+    ccfg = native_cfg(cfg)
+    dt_code = native.DTYPE_CODE[spec.dtype]
+    native.check(L.deca_gemm16_check_config(dt_code, M, N, K, ctypes.byref(ccfg)), f"gemm config {cfg}")
+    tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[spec.dtype]
+    cfg_ref = ctypes.byref(ccfg)
+    fn = L.deca_gemm16
+
+    def main(a, b, c):
+        _check_tensor(a, (M, K), tdt, "a")
+        _check_tensor(b, (K, N), tdt, "b")
+        _check_tensor(c, (M, N), tdt, "c")
+        native.check(fn(dt_code, a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, cfg_ref,
+                        current_stream_ptr()), "deca_gemm16")
+
+    main._keepalive = ccfg
+    return main

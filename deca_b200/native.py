@@ -1,0 +1,72 @@
+"""ctypes binding of libdeca_b200.so, the C ABI declared in include/deca_b200.h.
+
+There is no fallback: if the library is missing, loading raises, and every operator call
+goes through it.  Build it with ``python -m deca_b200.build``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+from .build import LIB_PATH
+
+_lib = None
+
+F16, BF16 = 0, 1
+SOFTMAX, RMSNORM = 0, 1
+ROW_REG, ROW_TWOPASS = 0, 1
+DTYPE_CODE = {"float16": F16, "bfloat16": BF16}
+ROW_OP_CODE = {"softmax": SOFTMAX, "rmsnorm": RMSNORM}
+ROW_MODE_CODE = {"reg": ROW_REG, "twopass": ROW_TWOPASS}
+
+
+class DecaError(RuntimeError):
+    def __init__(self, status: int, what: str):
+        self.status = status
+        super().__init__(f"{what}: status {status} ({status_string(status)})")
+
+
+class RowCfg(ctypes.Structure):
+    _fields_ = [
+        ("threads_per_row", ctypes.c_int),
+        ("rows_per_block", ctypes.c_int),
+        ("vec", ctypes.c_int),
+        ("mode", ctypes.c_int),
+        ("unroll", ctypes.c_int),
+        ("hint", ctypes.c_int),
+    ]
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: the CUDA kernels are not built and there is no fallback. "
+                "Run `python -m deca_b200.build`."
+            )
+        L = ctypes.CDLL(LIB_PATH)
+        L.deca_version.restype = ctypes.c_char_p
+        L.deca_status_string.restype = ctypes.c_char_p
+        L.deca_status_string.argtypes = [ctypes.c_int]
+        vp, i64, ci, cf = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
+        L.deca_rowwise.argtypes = [ci, ci, vp, vp, vp, i64, i64, cf, ctypes.POINTER(RowCfg), vp]
+        L.deca_rowwise_check_config.argtypes = [ci, ci, i64, i64, ctypes.POINTER(RowCfg)]
+        L.deca_rowwise_default_config.argtypes = [ci, ci, i64, i64, ctypes.POINTER(RowCfg)]
+        _lib = L
+    return _lib
+
+
+def version() -> str:
+    return lib().deca_version().decode()
+
+
+def status_string(status: int) -> str:
+    return lib().deca_status_string(int(status)).decode()
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        raise DecaError(status, what)

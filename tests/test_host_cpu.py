@@ -1,0 +1,134 @@
+"""CPU-only tests: the C-ABI library loads and exports what the header declares, the host-only
+entry points behave, and the Python mirror of the reference's operator surface reproduces the
+reference's records (golden_meta.json was written by the reference's own classes)."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def native():
+    from deca_b200 import build, native as n
+
+    build.build()
+    n.lib()
+    return n
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "deca_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(deca_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(native):
+    L = native.lib()
+    syms = declared_symbols()
+    assert "deca_rowwise" in syms and "deca_version" in syms
+    for s in syms:
+        assert hasattr(L, s), f"{s} is declared in include/deca_b200.h but not exported"
+    assert native.version().startswith("deca_b200")
+    assert native.status_string(0) == "ok"
+    assert "null" in native.status_string(-1)
+
+
+def test_rowwise_check_config_host_only(native):
+    L = native.lib()
+    ok = native.RowCfg(128, 2, 8, 0, 1, 0)
+    assert L.deca_rowwise_check_config(0, 0, 16384, 4096, ctypes.byref(ok)) == 0
+    for bad, code in (
+        (native.RowCfg(100, 1, 8, 0, 1, 0), -4),   # threads_per_row not a multiple of 32
+        (native.RowCfg(1024, 2, 8, 0, 1, 0), -4),  # more than 1024 threads
+        (native.RowCfg(128, 3, 8, 0, 1, 0), -4),   # rows_per_block does not divide M
+        (native.RowCfg(128, 1, 16, 0, 1, 0), -4),  # vector width
+        (native.RowCfg(32, 1, 8, 0, 1, 0), -4),    # 16 chunks is fine, but N=4096*4 needs 64 > 32
+        (native.RowCfg(128, 1, 8, 1, 3, 0), -4),   # unroll
+    ):
+        n = 16384 if bad.threads_per_row == 32 else 4096
+        assert L.deca_rowwise_check_config(0, 0, 16384, n, ctypes.byref(bad)) == code
+    assert L.deca_rowwise_check_config(0, 0, 16384, 4100, ctypes.byref(ok)) == -4  # N % vec
+    assert L.deca_rowwise_check_config(2, 0, 16, 64, ctypes.byref(ok)) == -5
+    assert L.deca_rowwise_check_config(0, 0, 16, 64, None) == -1
+    out = native.RowCfg()
+    for M, N in ((16384, 4096), (3, 1000), (1024, 128256), (7, 8), (65536, 1024)):
+        assert L.deca_rowwise_default_config(0, 0, M, N, ctypes.byref(out)) == 0
+        assert L.deca_rowwise_check_config(0, 0, M, N, ctypes.byref(out)) == 0
+
+
+def test_operator_records_match_reference(golden_meta):
+    from deca_b200.kernels import attn_bench, gemm_bench, rowwise_bench
+    from deca_b200.operators import GEMMTC, FlashAttention, RMSNorm, Softmax
+
+    for rec in golden_meta["gemmtc"]:
+        op = GEMMTC(*rec["shape"])
+        assert op.num_flops == rec["num_flops"]
+        assert list(op.tolerance) == pytest.approx(rec["tolerance"])
+        assert op.describe() == rec["describe"]
+    for rec in golden_meta["attention"]:
+        op = FlashAttention(*rec["shape"], causal=rec["causal"])
+        assert op.num_flops == rec["num_flops"]
+        assert op.softmax_scale == pytest.approx(rec["softmax_scale"])
+    for rec in golden_meta["rowwise"]:
+        cls = Softmax if rec["op"] == "softmax" else RMSNorm
+        op = cls(16384, 4096, rec["dtype_in"])
+        assert (op.dtype, op.num_bytes, list(op.tolerance), op.describe()) == (
+            rec["dtype"], rec["num_bytes"], rec["tolerance"], rec["describe"])
+    g = golden_meta["grids"]
+    assert [list(s) for s in gemm_bench.standard_shapes()] == g["gemm"]
+    assert [list(s) for s in attn_bench.standard_shapes()] == g["attention"]
+    assert [list(s) for s in rowwise_bench.standard_shapes("softmax")] == g["softmax"]
+    assert [list(s) for s in rowwise_bench.standard_shapes("rmsnorm")] == g["rmsnorm"]
+    assert attn_bench.attn_flops(4, 16, 4096, 4096, 128, True) == golden_meta["attn_flops_causal_4_16_4096_128"]
+
+
+def test_spec_files_round_trip(tmp_path):
+    from deca_b200.kernels.module import KernelSpec
+    from deca_b200.kernels.rowwise_b200 import RowConfig, build_rowwise_to_file, check_config
+
+    cfg = RowConfig(threads_per_row=256, rows_per_block=2, hint=True)
+    assert str(cfg) == "tpr=256,rpb=2,vec=8,mode=reg,hint=1"
+    assert str(RowConfig(mode="twopass", unroll=2)) == "tpr=128,rpb=1,vec=8,mode=twopass,unroll=2"
+    p = build_rowwise_to_file("rmsnorm", (16384, 4096), "bfloat16", cfg, 1e-5, "sm_100a", str(tmp_path / "cfg0.so"))
+    spec = KernelSpec.from_json(open(p).read())
+    assert spec.family == "rowwise" and spec.shape == (16384, 4096) and spec.params == {"op": "rmsnorm", "eps": 1e-5}
+    assert RowConfig(**spec.config) == cfg
+    with pytest.raises(AssertionError):
+        check_config(RowConfig(threads_per_row=48), "softmax", 16, 4096, "float16")
+    with pytest.raises(AssertionError):
+        check_config(RowConfig(rows_per_block=3), "softmax", 16, 4096, "float16")
+
+
+def test_python_and_native_config_rules_agree(native):
+    """Every config the Python rule accepts is accepted by the library's host check."""
+    import itertools
+
+    from deca_b200.kernels.rowwise_b200 import RowConfig, check_config, native_cfg
+
+    L = native.lib()
+    n_ok = 0
+    for tpr, rpb, vec, mode, unroll in itertools.product((32, 64, 128, 256, 512, 1024), (1, 2, 4, 8), (4, 8),
+                                                         ("reg", "twopass"), (1, 2, 4)):
+        cfg = RowConfig(tpr, rpb, vec, mode, unroll)
+        for M, N in ((16384, 4096), (1024, 128256), (24, 1000)):
+            try:
+                check_config(cfg, "softmax", M, N, "float16")
+            except AssertionError:
+                continue
+            n_ok += 1
+            c = native_cfg(cfg)
+            assert L.deca_rowwise_check_config(0, 0, M, N, ctypes.byref(c)) == 0, (cfg, M, N)
+    assert n_ok > 100
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from deca_b200 import native as n
+
+    monkeypatch.setattr(n, "_lib", None)
+    monkeypatch.setattr(n, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no fallback"):
+        n.lib()

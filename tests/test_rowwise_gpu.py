@@ -1,0 +1,190 @@
+"""GPU parity of the row-wise kernels against the CPU oracle, through the C ABI.
+
+Tolerance: 1e-3 relative against the oracle's fp32 value (see util.rowwise_allowed for the
+rounding terms), and at most one 16-bit ulp against the oracle's rounded output."""
+
+import ctypes
+
+import numpy as np
+import pytest
+
+import oracle
+from util import bits_to_torch, rowwise_allowed, torch_to_bits, ulp
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def native():
+    from deca_b200 import native as n
+
+    n.lib()
+    return n
+
+
+def make_x(M, N, dtype, seed=1, scale=3.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = scale * torch.randn(M, N, generator=g)
+    w = 1.0 + 0.1 * torch.randn(N, generator=g)
+    return oracle.to_bits(x.numpy(), dtype), oracle.to_bits(w.numpy(), dtype)
+
+
+def run_native(native, op, dtype, x_bits, w_bits, cfg=None, eps=1e-6):
+    """Calls deca_rowwise on device copies; the output sits between two canary rows."""
+    M, N = x_bits.shape
+    x = bits_to_torch(x_bits, dtype)
+    w = bits_to_torch(w_bits, dtype) if w_bits is not None else None
+    buf = torch.full((M + 2, N), 7.0, dtype=x.dtype, device="cuda")
+    y = buf[1 : M + 1]
+    ccfg = None
+    if cfg is not None:
+        ccfg = ctypes.byref(native.RowCfg(cfg["tpr"], cfg.get("rpb", 1), cfg.get("vec", 8),
+                                          native.ROW_MODE_CODE[cfg.get("mode", "reg")], cfg.get("unroll", 1),
+                                          int(cfg.get("hint", False))))
+    st = native.lib().deca_rowwise(
+        native.ROW_OP_CODE[op], native.DTYPE_CODE[dtype], x.data_ptr(), w.data_ptr() if w is not None else None,
+        y.data_ptr(), M, N, ctypes.c_float(eps), ccfg, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert st == 0, native.status_string(st)
+    assert torch.all(buf[0] == 7.0) and torch.all(buf[M + 1] == 7.0), "canary rows overwritten"
+    return torch_to_bits(y)
+
+
+def check(op, dtype, x_bits, w_bits, y_bits, eps=1e-6):
+    if op == "softmax":
+        ref_bits, ref32 = oracle.softmax(x_bits, dtype, want_f32=True)
+    else:
+        ref_bits, ref32 = oracle.rmsnorm(x_bits, w_bits, eps, dtype, want_f32=True)
+    got = oracle.from_bits(y_bits, dtype)
+    err = np.abs(got - ref32)
+    allowed = rowwise_allowed(ref32, dtype)
+    assert np.all(err <= allowed), f"max excess x{(err / allowed).max():.2f}"
+    ref = oracle.from_bits(ref_bits, dtype)
+    assert np.all(np.abs(got - ref) <= ulp(ref, dtype) * 1.0001)
+    assert np.mean(y_bits == ref_bits) > 0.97
+
+
+SHAPES = [(4, 4096), (3, 1000), (5, 8), (148 * 3, 1024), (64, 8192), (8, 32000), (2, 128256), (16, 2048), (7, 4104)]
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("op", ["softmax", "rmsnorm"])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_default_config_matches_oracle(native, op, dtype, shape):
+    x, w = make_x(*shape, dtype)
+    y = run_native(native, op, dtype, x, w if op == "rmsnorm" else None)
+    check(op, dtype, x, w, y)
+
+
+CONFIGS = [
+    dict(tpr=32, rpb=4), dict(tpr=64, rpb=1), dict(tpr=128, rpb=2, hint=True), dict(tpr=256, rpb=4),
+    dict(tpr=512, rpb=2), dict(tpr=1024, rpb=1), dict(tpr=128, rpb=1, vec=4), dict(tpr=256, rpb=1, vec=4, hint=True),
+    dict(tpr=128, mode="twopass", unroll=1), dict(tpr=128, mode="twopass", unroll=2, hint=True),
+    dict(tpr=64, mode="twopass", unroll=4, rpb=4), dict(tpr=256, mode="twopass", unroll=4, vec=4),
+]
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("op", ["softmax", "rmsnorm"])
+@pytest.mark.parametrize("cfg", CONFIGS, ids=lambda c: ",".join(f"{k}={v}" for k, v in c.items()))
+def test_configs_match_oracle(native, op, dtype, cfg):
+    for shape in ((8, 4096), (4, 5000)):
+        x, w = make_x(*shape, dtype, seed=5)
+        y = run_native(native, op, dtype, x, w if op == "rmsnorm" else None, cfg)
+        check(op, dtype, x, w, y)
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_golden_vectors(native, golden, dtype):
+    """Against the outputs of the reference's own torch code, with the reference's tolerance
+    (operators/Rowwise.py:15-20)."""
+    for tag in ("hid", "ragged", "vocab"):
+        x = golden[f"row_{tag}_{dtype}_x"]
+        ref = oracle.from_bits(golden[f"row_{tag}_{dtype}_softmax"], dtype)
+        got = oracle.from_bits(run_native(native, "softmax", dtype, x, None), dtype)
+        rtol = 1e-2 if dtype == "float16" else 3e-2
+        assert np.all(np.abs(got - ref) <= 1e-5 + rtol * np.abs(ref))
+        assert np.all(np.abs(got - ref) <= ulp(ref, dtype) * 1.0001)
+        if tag == "vocab":
+            continue
+        w = golden[f"row_{tag}_{dtype}_w"]
+        ref = oracle.from_bits(golden[f"row_{tag}_{dtype}_rmsnorm"], dtype)
+        got = oracle.from_bits(run_native(native, "rmsnorm", dtype, x, w), dtype)
+        tol = 1e-2 if dtype == "float16" else 3e-2
+        assert np.all(np.abs(got - ref) <= tol + tol * np.abs(ref))
+        assert np.all(np.abs(got - ref) <= 1.5 * ulp(ref, dtype))
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_full_size_properties(native, dtype):
+    """The benchmark shape X[16384, 4096]: size-independent properties on every row, the
+    oracle on a sample of rows, and bit-identical reruns."""
+    M, N = 16384, 4096
+    g = torch.Generator(device="cpu").manual_seed(1)
+    tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[dtype]
+    x = (3.0 * torch.randn(M, N, generator=g)).to(tdt).cuda()
+    w = (1.0 + 0.1 * torch.randn(N, generator=g)).to(tdt).cuda()
+    from deca_b200.operators import RMSNorm, Softmax
+
+    sm, rn = Softmax(M, N, dtype), RMSNorm(M, N, dtype, 1e-6)
+    y = sm(x)
+    torch.cuda.synchronize()
+    yf = y.float()
+    assert torch.all(yf >= 0)
+    assert torch.allclose(yf.sum(-1), torch.ones(M, device="cuda"), atol=4e-3 if dtype == "float16" else 2e-2)
+    assert torch.equal(yf.argmax(-1), x.float().argmax(-1)) or torch.all(
+        x.float().gather(1, yf.argmax(-1, keepdim=True)) == x.float().max(-1, keepdim=True).values)
+    # softmax is invariant to a per-row shift that is exact in the 16-bit type
+    assert torch.equal(sm(x), y)
+    z = rn(x, w)
+    torch.cuda.synchronize()
+    assert torch.equal(rn(x, w), z)
+    # RMSNorm is homogeneous of degree 0 in x for power-of-two scales (eps aside)
+    z2 = rn((x.float() * 2).to(tdt), w)
+    assert (z2.float() - z.float()).abs().max().item() <= 2e-2 * z.float().abs().max().item()
+    rows = torch.randint(0, M, (48,), generator=torch.Generator().manual_seed(0))
+    xb, wb = torch_to_bits(x[rows.cuda()]), torch_to_bits(w)
+    check("softmax", dtype, xb, None, torch_to_bits(y[rows.cuda()]))
+    check("rmsnorm", dtype, xb, wb, torch_to_bits(z[rows.cuda()]))
+    # and the reference's own acceptance test: eager torch within its tolerance table
+    for op, out, inputs in ((sm, y, (x,)), (rn, z, (x, w))):
+        ref = op.reference(inputs).float()
+        atol, rtol = op.tolerance
+        assert torch.all((out.float() - ref).abs() <= atol + rtol * ref.abs())
+
+
+def test_edge_values(native):
+    """Rows with -inf entries, constant rows and a large dynamic range."""
+    N = 1024
+    x = np.zeros((4, N), np.float32)
+    x[0, :] = 5.0
+    x[1, :] = -np.inf
+    x[1, 7] = 1.0
+    x[2, :] = np.linspace(-60000, 60000, N)
+    x[3, ::2] = -np.inf
+    for dtype in ("float16", "bfloat16"):
+        xb = oracle.to_bits(x, dtype)
+        y = oracle.from_bits(run_native(native, "softmax", dtype, xb, None), dtype)
+        ref = oracle.from_bits(oracle.softmax(xb, dtype), dtype)
+        assert np.all(np.abs(y - ref) <= ulp(ref, dtype) * 1.0001)
+        assert y[1, 7] == 1.0 and y[1].sum() == 1.0
+
+
+def test_argument_errors(native):
+    L = native.lib()
+    x = torch.zeros(8, 64, dtype=torch.float16, device="cuda")
+    y = torch.empty_like(x)
+    st = ctypes.c_void_p(0)
+    f = ctypes.c_float(1e-6)
+    assert L.deca_rowwise(0, 0, None, None, y.data_ptr(), 8, 64, f, None, st) == -1
+    assert L.deca_rowwise(1, 0, x.data_ptr(), None, y.data_ptr(), 8, 64, f, None, st) == -1
+    assert L.deca_rowwise(0, 0, x.data_ptr(), None, y.data_ptr(), 0, 64, f, None, st) == -2
+    assert L.deca_rowwise(0, 0, x.data_ptr() + 2, None, y.data_ptr(), 4, 64, f, None, st) == -3
+    assert L.deca_rowwise(0, 7, x.data_ptr(), None, y.data_ptr(), 8, 64, f, None, st) == -5
+    bad = native.RowCfg(48, 1, 8, 0, 1, 0)
+    assert L.deca_rowwise(0, 0, x.data_ptr(), None, y.data_ptr(), 8, 64, f, ctypes.byref(bad), st) == -4
+    bad = native.RowCfg(32, 3, 8, 0, 1, 0)  # rows_per_block does not divide M
+    assert L.deca_rowwise(0, 0, x.data_ptr(), None, y.data_ptr(), 8, 64, f, ctypes.byref(bad), st) == -4
+    torch.cuda.synchronize()
