@@ -172,11 +172,15 @@ class RowwiseWorkload:
         x, w = self.dev[dt]
         return (x, self.out[key]) if kind == "softmax" else (x, w, self.out[key])
 
-    def step(self, events=None):
-        for i, (key, _, main) in enumerate(self.ops):
+    def step(self):
+        for key, _, main in self.ops:
             main(*self.args_for(key))
-            if events is not None:
-                events[i].record()
+
+    dominant_reps = 8
+
+    def dominant_launch(self):
+        key, _, main = self.ops[0]
+        main(*self.args_for(key))
 
     def step_e2e(self):
         """Host pinned inputs -> device -> operator call -> host pinned outputs."""
@@ -266,6 +270,7 @@ def main():
     ap.add_argument("--workload", default="rowwise")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-graph", action="store_true", help="launch from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -311,24 +316,58 @@ def main():
         wl.step()
     barrier()
 
-    # ---- timed region: K steps, one event after every launch ----
+    # One step (and, for the roofline, the dominant kernel alone) is captured into a CUDA graph
+    # so that the timed region holds kernel launches only, no Python between them.
+    step_graph = dom_graph = None
+    if not args.no_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(step_graph, stream=side):
+                wl.step()
+            dom_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(dom_graph, stream=side):
+                for _ in range(wl.dominant_reps):
+                    wl.dominant_launch()
+        torch.cuda.current_stream().wait_stream(side)
+        step_graph.replay()
+        dom_graph.replay()
+    barrier()
+
+    def run_step():
+        step_graph.replay() if step_graph is not None else wl.step()
+
+    def run_dominant():
+        if dom_graph is not None:
+            dom_graph.replay()
+        else:
+            for _ in range(wl.dominant_reps):
+                wl.dominant_launch()
+
+    # ---- timed region: exactly K steps between two events ----
     L = wl.launches_per_step
-    start = torch.cuda.Event(enable_timing=True)
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(L)] for _ in range(args.steps)]
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clk:
         barrier()
         start.record()
-        for s in range(args.steps):
-            wl.step(evs[s])
+        for _ in range(args.steps):
+            run_step()
+        end.record()
         torch.cuda.synchronize()
-    barrier()
-    total_ms = start.elapsed_time(evs[-1][-1])
-    # per-launch durations of the dominant kernel (launch 0 of each step): previous event -> its event
-    dom_ms = []
-    for s in range(args.steps):
-        prev = start if s == 0 else evs[s - 1][-1]
-        dom_ms.append(prev.elapsed_time(evs[s][0]))
-    dom_avg_ms = sum(dom_ms) / len(dom_ms)
+        barrier()
+        total_ms = start.elapsed_time(end)
+        # ---- the dominant kernel alone, back to back, for the roofline ----
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dom_iters = max(1, args.steps // 4)
+        run_dominant()
+        torch.cuda.synchronize()
+        d0.record()
+        for _ in range(dom_iters):
+            run_dominant()
+        d1.record()
+        torch.cuda.synchronize()
+        dom_avg_ms = d0.elapsed_time(d1) / (dom_iters * wl.dominant_reps)
 
     t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
     if dist is not None:
@@ -364,7 +403,7 @@ def main():
             "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config,
             "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": L * args.steps,
+            "gpu_launches": L * args.steps, "launch_mode": "python" if args.no_graph else "cuda_graph",
             "roofline": {"bound": wl.bound, "kernel": f"{wl.dominant[0]} {wl.dominant[1]}", "achieved": achieved,
                          "peak": peak, "unit": punit, "frac": achieved / peak, "peak_source": peaks["source"],
                          "avg_launch_us": dom_avg_ms * 1e3, "traffic": NCU_TRAFFIC_BYTES.get(wl.traffic_key)},

@@ -1,5 +1,44 @@
 // Library-level entry points of the C ABI: version and status text.
-#include "common.cuh"
+#include <mutex>
+
+#include "ptx.cuh"
+
+namespace deca {
+
+__device__ DeviceStatus g_device_status = {0u, 0u, 0u, 0u};
+
+DeviceStatus *device_status_ptr() {
+    // The symbol has one address per device; cache them.
+    static std::mutex mu;
+    static DeviceStatus *ptrs[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptrs[dev]) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+        ptrs[dev] = static_cast<DeviceStatus *>(p);
+    }
+    return ptrs[dev];
+}
+
+}  // namespace deca
+
+extern "C" int deca_last_device_status(int *code, int *where, int *block, int clear) {
+    deca::DeviceStatus *p = deca::device_status_ptr();
+    if (!p) return (int)cudaErrorUnknown;
+    deca::DeviceStatus h;
+    cudaError_t e = cudaMemcpy(&h, p, sizeof(h), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return (int)e;
+    if (code) *code = (int)h.code;
+    if (where) *where = (int)h.where;
+    if (block) *block = (int)h.block;
+    if (clear && h.code != 0) {
+        e = cudaMemset(p, 0, sizeof(h));
+        if (e != cudaSuccess) return (int)e;
+    }
+    return DECA_OK;
+}
 
 extern "C" const char *deca_version(void) { return "deca_b200 0.1 (sm_100a)"; }
 

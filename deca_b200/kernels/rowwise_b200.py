@@ -16,9 +16,13 @@ LOG2E = 1.4426950408889634
 NEG_INF = -1e30
 OPS = ("softmax", "rmsnorm")
 DTYPES = ("float16", "bfloat16")
-MODES = ("reg", "twopass")
+MODES = ("reg", "twopass", "tma")
 MAX_REGS_PER_SM = 65536
 MAX_REG_CHUNKS = 32  # chunk counts the register-mode kernels are instantiated for
+MAX_TMA_CHUNKS = 16
+TMA_MAX_THREADS = 512
+TMA_OUT_SLOTS = 2
+MAX_DYN_SMEM = 232448
 KEEP_EXP_ELEMS = 128  # softmax keeps the exponentials in fp32 registers up to this many elements
 
 
@@ -28,7 +32,8 @@ class RowConfig:
     rows_per_block: int = 1
     vec: int = 8  # elements per vector access (8 -> 16 B for 16-bit dtypes)
     mode: str = "reg"
-    unroll: int = 1  # chunks loaded back to back per twopass iteration
+    # twopass: chunks loaded back to back per iteration; tma: rows in flight per row group
+    unroll: int = 1
     hint: bool = False  # no-allocate loads and streaming stores
 
     @property
@@ -40,7 +45,7 @@ class RowConfig:
 
     def __str__(self):
         s = f"tpr={self.threads_per_row},rpb={self.rows_per_block},vec={self.vec},mode={self.mode}"
-        s += f",unroll={self.unroll}" if self.mode == "twopass" else ""
+        s += f",unroll={self.unroll}" if self.mode in ("twopass", "tma") else ""
         return s + (",hint=1" if self.hint else "")
 
 
@@ -55,7 +60,7 @@ def est_regs_per_thread(cfg: RowConfig, N: int, op: str) -> int:
     keeps the exponentials in fp32 up to KEEP_EXP_ELEMS elements (one register each, the packed
     copy dies as they are produced); RMSNorm keeps only the packed row plus one weight chunk.
     """
-    if cfg.mode == "reg":
+    if cfg.mode in ("reg", "tma"):
         elems = num_chunks(cfg, N) * cfg.vec
         if op == "softmax":
             regs = (elems if elems <= KEEP_EXP_ELEMS else elems // 2 + cfg.vec) + 24
@@ -67,8 +72,25 @@ def est_regs_per_thread(cfg: RowConfig, N: int, op: str) -> int:
     return regs
 
 
+def tma_smem_bytes(cfg: RowConfig, op: str, N: int) -> int:
+    """Dynamic shared memory of the bulk-copy mode: barriers + the weight row (RMSNorm) + per
+    row group an input ring of ``unroll`` rows and an output ring of two."""
+    pitch = -(-N * 2 // 128) * 128
+    return 2048 + (pitch if op == "rmsnorm" else 0) + cfg.rows_per_block * (cfg.unroll + TMA_OUT_SLOTS) * pitch
+
+
 def check_config(cfg: RowConfig, op: str, M: int, N: int, dtype: str) -> None:
     assert op in OPS and dtype in DTYPES and cfg.mode in MODES
+    if cfg.mode == "tma":
+        # persistent CTAs; `rows_per_block` independent row groups, `unroll` rows in flight each
+        tpr = cfg.threads_per_row
+        assert cfg.vec == 8 and N % 8 == 0
+        assert 32 <= tpr <= TMA_MAX_THREADS and tpr & (tpr - 1) == 0
+        assert 1 <= cfg.rows_per_block <= 15 and cfg.threads <= TMA_MAX_THREADS
+        assert 1 <= cfg.unroll <= 8 and cfg.rows_per_block * cfg.unroll <= 64
+        assert num_chunks(cfg, N) <= MAX_TMA_CHUNKS
+        assert tma_smem_bytes(cfg, op, N) <= MAX_DYN_SMEM
+        return
     assert cfg.vec in (4, 8) and N % cfg.vec == 0
     assert cfg.threads_per_row % 32 == 0 and cfg.threads_per_row >= 32 and cfg.threads <= 1024
     assert cfg.rows_per_block >= 1 and M % cfg.rows_per_block == 0

@@ -15,10 +15,11 @@ _lib = None
 
 F16, BF16 = 0, 1
 SOFTMAX, RMSNORM = 0, 1
-ROW_REG, ROW_TWOPASS = 0, 1
+ROW_REG, ROW_TWOPASS, ROW_TMA = 0, 1, 2
 DTYPE_CODE = {"float16": F16, "bfloat16": BF16}
 ROW_OP_CODE = {"softmax": SOFTMAX, "rmsnorm": RMSNORM}
-ROW_MODE_CODE = {"reg": ROW_REG, "twopass": ROW_TWOPASS}
+ROW_MODE_CODE = {"reg": ROW_REG, "twopass": ROW_TWOPASS, "tma": ROW_TMA}
+ROW_MODE_NAME = {v: k for k, v in ROW_MODE_CODE.items()}
 
 
 class DecaError(RuntimeError):
@@ -38,6 +39,10 @@ class RowCfg(ctypes.Structure):
     ]
 
 
+class GemmCfg(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in ("BM", "BN", "BK", "stages", "raster", "epi_smem", "cta_group", "acc_bufs")]
+
+
 def lib() -> ctypes.CDLL:
     """The loaded library; raises if it has not been built."""
     global _lib
@@ -55,6 +60,10 @@ def lib() -> ctypes.CDLL:
         L.deca_rowwise.argtypes = [ci, ci, vp, vp, vp, i64, i64, cf, ctypes.POINTER(RowCfg), vp]
         L.deca_rowwise_check_config.argtypes = [ci, ci, i64, i64, ctypes.POINTER(RowCfg)]
         L.deca_rowwise_default_config.argtypes = [ci, ci, i64, i64, ctypes.POINTER(RowCfg)]
+        L.deca_gemm16_check_config.argtypes = [ci, i64, i64, i64, ctypes.POINTER(GemmCfg)]
+        L.deca_gemm16.argtypes = [ci, vp, vp, vp, i64, i64, i64, ctypes.POINTER(GemmCfg), vp]
+        ip = ctypes.POINTER(ci)
+        L.deca_last_device_status.argtypes = [ip, ip, ip, ci]
         _lib = L
     return _lib
 
@@ -70,3 +79,12 @@ def status_string(status: int) -> str:
 def check(status: int, what: str) -> None:
     if status != 0:
         raise DecaError(status, what)
+
+
+def last_device_status(clear: bool = True):
+    """(code, where, block) of the first bounded wait that ran out since the last clear;
+    code 0 means none.  Synchronises the device."""
+    c, w, b = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+    check(lib().deca_last_device_status(ctypes.byref(c), ctypes.byref(w), ctypes.byref(b), int(clear)),
+          "deca_last_device_status")
+    return c.value, w.value, b.value

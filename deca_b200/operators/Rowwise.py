@@ -66,8 +66,8 @@ class RowwiseOperator(Operator):
             ),
             "deca_rowwise_default_config",
         )
-        mode = "twopass" if c.mode == native.ROW_TWOPASS else "reg"
-        return RowConfig(c.threads_per_row, c.rows_per_block, c.vec, mode, c.unroll, bool(c.hint))
+        return RowConfig(c.threads_per_row, c.rows_per_block, c.vec, native.ROW_MODE_NAME[c.mode], c.unroll,
+                         bool(c.hint))
 
     def __call__(self, *inputs, out=None, cfg: RowConfig | None = None):
         """Runs the kernel on ``inputs`` (x[, w]); returns y."""

@@ -1,0 +1,140 @@
+"""GPU parity of the tcgen05 GEMM against the CPU oracle, through the C ABI.
+
+Tolerance: |c - c32| <= 1e-2 + 1e-2 * |c32| against the oracle's fp32-accumulated result (the
+stated bound), and the reference's own tighter acceptance bound atol = 1e-2 * sqrt(K / 1024),
+rtol = 2e-3 (operators/GEMMTC.py:51-63; bf16 uses one bf16 ulp, 1.6e-2, as rtol)."""
+
+import ctypes
+import math
+
+import numpy as np
+import pytest
+
+import oracle
+from util import bits_to_torch, torch_to_bits
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def native():
+    from deca_b200 import native as n
+
+    n.lib()
+    return n
+
+
+def make_ab(M, N, K, dtype, seed=2):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    a = torch.rand(M, K, generator=g) * 2 - 1
+    b = torch.rand(K, N, generator=g) * 2 - 1
+    return oracle.to_bits(a.numpy(), dtype), oracle.to_bits(b.numpy(), dtype)
+
+
+def run_native(native, dtype, a_bits, b_bits, cfg=None):
+    M, K = a_bits.shape
+    N = b_bits.shape[1]
+    a, b = bits_to_torch(a_bits, dtype), bits_to_torch(b_bits, dtype)
+    buf = torch.full((M + 2, N), 7.0, dtype=a.dtype, device="cuda")
+    c = buf[1 : M + 1]
+    ccfg = None
+    if cfg is not None:
+        ccfg = ctypes.byref(native.GemmCfg(128, cfg.get("BN", 256), 64, cfg.get("stages", 4), cfg.get("raster", 8),
+                                           cfg.get("epi_smem", 1), 1, cfg.get("acc_bufs", 2)))
+    st = native.lib().deca_gemm16(native.DTYPE_CODE[dtype], a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, ccfg,
+                                  ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert st == 0, native.status_string(st)
+    assert native.last_device_status() == (0, 0, 0)
+    assert torch.all(buf[0] == 7.0) and torch.all(buf[M + 1] == 7.0), "canary rows overwritten"
+    return torch_to_bits(c)
+
+
+def check(dtype, a_bits, b_bits, c_bits):
+    K = a_bits.shape[1]
+    _, c32 = oracle.gemm16(a_bits, b_bits, dtype, want_f32=True)
+    got = oracle.from_bits(c_bits, dtype)
+    err = np.abs(got - c32)
+    assert np.all(err <= 1e-2 + 1e-2 * np.abs(c32)), f"max err {err.max()}"
+    atol, rtol = 1e-2 * math.sqrt(max(K, 64) / 1024), (2e-3 if dtype == "float16" else 1.6e-2)
+    assert np.all(err <= atol + rtol * np.abs(c32)), f"max err {err.max()} (reference bound)"
+
+
+SHAPES = [(128, 256, 64), (128, 256, 128), (128, 64, 512), (256, 512, 256), (384, 768, 320), (64, 80, 96),
+          (200, 264, 136), (1, 8, 8), (1000, 1000, 1000), (130, 2056, 72), (2048, 256, 64)]
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_default_config_matches_oracle(native, dtype, shape):
+    M, N, K = shape
+    a, b = make_ab(M, N, K, dtype)
+    check(dtype, a, b, run_native(native, dtype, a, b))
+
+
+CONFIGS = [
+    dict(BN=64, stages=2, acc_bufs=1, epi_smem=0), dict(BN=64, stages=8, acc_bufs=2), dict(BN=128, stages=3, raster=1),
+    dict(BN=128, stages=6, acc_bufs=1), dict(BN=256, stages=2, epi_smem=0), dict(BN=256, stages=3, acc_bufs=1),
+    dict(BN=256, stages=4, raster=2), dict(BN=128, stages=4, epi_smem=0, raster=16),
+]
+
+
+@pytest.mark.parametrize("cfg", CONFIGS, ids=lambda c: ",".join(f"{k}={v}" for k, v in c.items()))
+def test_configs_match_oracle(native, cfg):
+    for shape in ((640, 768, 448), (300, 520, 200)):
+        a, b = make_ab(*shape, "float16", seed=7)
+        check("float16", a, b, run_native(native, "float16", a, b, cfg))
+
+
+def test_golden_vector(native, golden):
+    """A, B and the fp32 result of the reference's own GEMMTC.reference."""
+    c = oracle.from_bits(run_native(native, "float16", golden["gemm_a"], golden["gemm_b"]), "float16")
+    ref = golden["gemm_c32"]
+    assert np.all(np.abs(c - ref) <= 2.5e-3 + 2e-3 * np.abs(ref))  # GEMMTC(64, 80, 96).tolerance
+
+
+@pytest.mark.parametrize("size", [4096])
+def test_full_size_against_torch_and_oracle(native, size):
+    """The benchmark shape: every element against torch's fp32 GEMM of the same inputs (the
+    reference's acceptance test), sampled rows against the oracle, linearity, determinism."""
+    from deca_b200.operators import GEMMTC
+
+    M = N = K = size
+    g = torch.Generator(device="cpu").manual_seed(2)
+    a = (torch.rand(M, K, generator=g) * 2 - 1).half().cuda()
+    b = (torch.rand(K, N, generator=g) * 2 - 1).half().cuda()
+    op = GEMMTC(M, N, K)
+    c = op(a, b)
+    torch.cuda.synchronize()
+    ref = op.reference((a, b))
+    atol, rtol = op.tolerance
+    assert torch.all((c.float() - ref).abs() <= atol + rtol * ref.abs())
+    assert torch.all((c.float() - ref).abs() <= 1e-2 + 1e-2 * ref.abs())
+    assert torch.equal(op(a, b), c)
+    rows = torch.randint(0, M, (8,), generator=torch.Generator().manual_seed(0)).cuda()
+    check("float16", torch_to_bits(a[rows]), torch_to_bits(b), torch_to_bits(c[rows]))
+    # linearity: (2A) B == 2 (A B) exactly (scaling by two is exact in fp16 and fp32) wherever
+    # the result is a normal fp16 number (subnormal results round on a fixed absolute grid)
+    c2 = op((a * 2).half(), b)
+    normal = c.float().abs() >= 2.0**-13
+    assert torch.equal(c2.float()[normal], (c.float() * 2)[normal])
+
+
+def test_argument_errors(native):
+    L = native.lib()
+    a = torch.zeros(128, 64, dtype=torch.float16, device="cuda")
+    b = torch.zeros(64, 64, dtype=torch.float16, device="cuda")
+    c = torch.zeros(128, 64, dtype=torch.float16, device="cuda")
+    st = ctypes.c_void_p(0)
+    assert L.deca_gemm16(0, None, b.data_ptr(), c.data_ptr(), 128, 64, 64, None, st) == -1
+    assert L.deca_gemm16(0, a.data_ptr(), b.data_ptr(), c.data_ptr(), 0, 64, 64, None, st) == -2
+    assert L.deca_gemm16(0, a.data_ptr(), b.data_ptr(), c.data_ptr(), 128, 60, 64, None, st) == -3
+    assert L.deca_gemm16(0, a.data_ptr() + 2, b.data_ptr(), c.data_ptr(), 64, 64, 64, None, st) == -3
+    assert L.deca_gemm16(3, a.data_ptr(), b.data_ptr(), c.data_ptr(), 128, 64, 64, None, st) == -5
+    bad = native.GemmCfg(128, 96, 64, 4, 8, 1, 1, 2)
+    assert L.deca_gemm16(0, a.data_ptr(), b.data_ptr(), c.data_ptr(), 128, 64, 64, ctypes.byref(bad), st) == -4
+    bad = native.GemmCfg(128, 256, 64, 8, 8, 1, 1, 2)  # 8 stages of 48 KB do not fit shared memory
+    assert L.deca_gemm16(0, a.data_ptr(), b.data_ptr(), c.data_ptr(), 128, 64, 64, ctypes.byref(bad), st) == -4
+    torch.cuda.synchronize()

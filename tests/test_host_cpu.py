@@ -112,7 +112,7 @@ def test_python_and_native_config_rules_agree(native):
     L = native.lib()
     n_ok = 0
     for tpr, rpb, vec, mode, unroll in itertools.product((32, 64, 128, 256, 512, 1024), (1, 2, 4, 8), (4, 8),
-                                                         ("reg", "twopass"), (1, 2, 4)):
+                                                         ("reg", "twopass", "tma"), (1, 2, 4)):
         cfg = RowConfig(tpr, rpb, vec, mode, unroll)
         for M, N in ((16384, 4096), (1024, 128256), (24, 1000)):
             try:

