@@ -43,6 +43,10 @@ class GemmCfg(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in ("BM", "BN", "BK", "stages", "raster", "epi_smem", "cta_group", "acc_bufs")]
 
 
+class FaCfg(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in ("Br", "Bc", "stages", "q_tiles")]
+
+
 def lib() -> ctypes.CDLL:
     """The loaded library; raises if it has not been built."""
     global _lib
@@ -62,6 +66,8 @@ def lib() -> ctypes.CDLL:
         L.deca_rowwise_default_config.argtypes = [ci, ci, i64, i64, ctypes.POINTER(RowCfg)]
         L.deca_gemm16_check_config.argtypes = [ci, i64, i64, i64, ctypes.POINTER(GemmCfg)]
         L.deca_gemm16.argtypes = [ci, vp, vp, vp, i64, i64, i64, ctypes.POINTER(GemmCfg), vp]
+        L.deca_fa_fwd_f16_check_config.argtypes = [ci, ci, ci, ci, ci, ci, ctypes.POINTER(FaCfg)]
+        L.deca_fa_fwd_f16.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, ctypes.POINTER(FaCfg), vp]
         ip = ctypes.POINTER(ci)
         L.deca_last_device_status.argtypes = [ip, ip, ip, ci]
         _lib = L

@@ -41,7 +41,7 @@ def run_native(native, dtype, a_bits, b_bits, cfg=None):
     c = buf[1 : M + 1]
     ccfg = None
     if cfg is not None:
-        ccfg = ctypes.byref(native.GemmCfg(128, cfg.get("BN", 256), 64, cfg.get("stages", 4), cfg.get("raster", 8),
+        ccfg = ctypes.byref(native.GemmCfg(cfg.get("BM", 128), cfg.get("BN", 256), 64, cfg.get("stages", 4), cfg.get("raster", 8),
                                            cfg.get("epi_smem", 1), 1, cfg.get("acc_bufs", 2)))
     st = native.lib().deca_gemm16(native.DTYPE_CODE[dtype], a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, ccfg,
                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
@@ -78,14 +78,18 @@ CONFIGS = [
     dict(BN=64, stages=2, acc_bufs=1, epi_smem=0), dict(BN=64, stages=8, acc_bufs=2), dict(BN=128, stages=3, raster=1),
     dict(BN=128, stages=6, acc_bufs=1), dict(BN=256, stages=2, epi_smem=0), dict(BN=256, stages=3, acc_bufs=1),
     dict(BN=256, stages=4, raster=2), dict(BN=128, stages=4, epi_smem=0, raster=16),
+    dict(BM=256, BN=256, stages=3, acc_bufs=1), dict(BM=256, BN=256, stages=2, acc_bufs=1, epi_smem=0, raster=1),
+    dict(BM=256, BN=128, stages=4, acc_bufs=2), dict(BM=256, BN=128, stages=4, acc_bufs=1, raster=3),
 ]
 
 
 @pytest.mark.parametrize("cfg", CONFIGS, ids=lambda c: ",".join(f"{k}={v}" for k, v in c.items()))
 def test_configs_match_oracle(native, cfg):
-    for shape in ((640, 768, 448), (300, 520, 200)):
+    for shape in ((640, 768, 448), (300, 520, 200), (1280, 1024, 128)):
         a, b = make_ab(*shape, "float16", seed=7)
         check("float16", a, b, run_native(native, "float16", a, b, cfg))
+    a, b = make_ab(520, 264, 328, "bfloat16", seed=8)
+    check("bfloat16", a, b, run_native(native, "bfloat16", a, b, cfg))
 
 
 def test_golden_vector(native, golden):
