@@ -38,7 +38,14 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/ (None until a capture exists for that kernel).
 NCU_TRAFFIC_BYTES = {
-    "rowwise_softmax_f16_16384x4096": None,
+    # profiles/rowwise_softmax_f16_16384x4096.md: 134.23 MB read + 83.40 MB written (part of the
+    # output is still dirty in L2 when the kernel ends)
+    "rowwise_softmax_f16_16384x4096": 217628672,
+    # profiles/gemm_f16_4096.md: 80.51 MB read + 6.59 MB written (C mostly still in L2)
+    "gemm_f16_4096x4096x4096": 87099392,
+    # profiles/fa_fwd_f16_1x16x4096x128.md captured B = 1 (50.38 MB + 1.50 MB); traffic grows
+    # in proportion to the batch: x 4 for B = 4
+    "fa_fwd_f16_4x16x4096x128": 207522816,
 }
 
 
@@ -137,9 +144,10 @@ class RowwiseWorkload:
     unit = "TB/s"
     dtype = "f32 math, f16/bf16 I/O"
     bound = "hbm"
+    scaling = "weak"
     M, N, EPS = 16384, 4096, 1e-6
 
-    def __init__(self, rank: int):
+    def __init__(self, rank: int, world: int = 1):
         import torch
 
         from deca_b200.operators import RMSNorm, Softmax
@@ -231,6 +239,228 @@ class RowwiseWorkload:
         return once, reps, nbytes_once, sample, np
 
 
+class GemmWorkload:
+    """fp16 tensor-core GEMM, A, B ~ U[-1, 1] (seed 2).  One step = one GEMM on each of
+    `sets` rotating (A, B, C) buffer sets, so that more than an L2 of other data passes between
+    two uses of a buffer."""
+
+    name = "fp16 GEMM M=N=K=4096"
+    metric = "fp16 tensor-core GEMM throughput (2*M*N*K flops)"
+    unit = "TFLOPS"
+    dtype = "f16 x f16 -> f32 accumulate, f16 out"
+    bound = "tensor"
+    scaling = "weak"
+    shape = (4096, 4096, 4096)
+    sets = 4
+    shard_m = False
+    seed = 2
+
+    def __init__(self, rank: int, world: int = 1):
+        import torch
+
+        from deca_b200.operators import GEMMTC
+
+        M, N, K = self.shape
+        if self.shard_m:
+            assert M % world == 0
+            M //= world
+        self.M, self.N, self.K = M, N, K
+        self.op = GEMMTC(M, N, K)
+        self.cfg = self.op.default_config()
+        self.main = self.op.compile(self.op.build_mod(self.cfg))["main"]
+        g = torch.Generator(device="cpu").manual_seed(self.seed + 1000 * rank)
+        self.host, self.dev = [], []
+        for i in range(self.sets):
+            if i == 0 or not self.shard_m:
+                a = (torch.rand(M, K, generator=g) * 2 - 1).half()
+                b = (torch.rand(K, N, generator=g) * 2 - 1).half()
+            self.dev.append((a.cuda(), b.cuda(), torch.empty(M, N, dtype=torch.float16, device="cuda")))
+        # e2e uses pinned copies of the first set only
+        self.host = (self.dev[0][0].cpu().pin_memory(), self.dev[0][1].cpu().pin_memory(),
+                     torch.empty(M, N, dtype=torch.float16).pin_memory())
+        self.units_per_step = self.sets * self.op.num_flops
+        self.launches_per_step = self.sets
+        self.dominant = ("gemm16", str(self.cfg))
+        self.dominant_units = self.op.num_flops
+        self.traffic_key = f"gemm_f16_{M}x{N}x{K}"
+        self.dominant_reps = self.sets
+        self._rr = 0
+        self.config = {"workload": self.name, "M_per_gpu": M, "N": N, "K": K, "kernel_config": str(self.cfg),
+                       "l2": f"{self.sets} rotating buffer sets ({self.sets * (M * K + K * N + M * N) * 2 >> 20} MiB)"}
+
+    def step(self):
+        for a, b, c in self.dev:
+            self.main(a, b, c)
+
+    def dominant_launch(self):
+        a, b, c = self.dev[self._rr % self.sets]
+        self._rr += 1
+        self.main(a, b, c)
+
+    def step_e2e(self):
+        ha, hb, hc = self.host
+        a, b, c = self.dev[0]
+        h2d = d2h = 0
+        for _ in range(self.sets):
+            a.copy_(ha, non_blocking=True)
+            b.copy_(hb, non_blocking=True)
+            self.op(a, b, out=c)
+            hc.copy_(c, non_blocking=True)
+            h2d += (ha.numel() + hb.numel()) * 2
+            d2h += hc.numel() * 2
+        return h2d, d2h
+
+    def to_value(self, units_per_s):
+        return units_per_s / 1e12
+
+    roofline_value = to_value
+
+    def cpu_sample(self, target_s=12.0):
+        import numpy as np
+        import torch
+
+        import oracle
+
+        _, N, K = self.shape
+        g = torch.Generator(device="cpu").manual_seed(self.seed)
+        rows = 64
+        a = oracle.to_bits((torch.rand(rows, K, generator=g) * 2 - 1).numpy(), "float16")
+        b = oracle.to_bits((torch.rand(K, N, generator=g) * 2 - 1).numpy(), "float16")
+
+        def once():
+            oracle.gemm16(a, b, "float16")
+
+        once()
+        t0 = time.perf_counter()
+        once()
+        t1 = time.perf_counter() - t0
+        reps = max(1, int(target_s / max(t1, 1e-3)))
+        sample = f"{reps} x ({rows} rows of A) @ B[{K},{N}], fp32 accumulate"
+        return once, reps, 2 * rows * N * K, sample, np
+
+
+class GemmShardedWorkload(GemmWorkload):
+    """The multi-GPU GEMM configuration: M = 65536 split along M across the ranks (strong
+    scaling), B replicated, no collective."""
+
+    name = "fp16 GEMM M=65536 N=8192 K=8192 split along M"
+    shape = (65536, 8192, 8192)
+    sets = 1
+    shard_m = True
+    scaling = "strong"
+    seed = 4
+
+
+class AttentionWorkload:
+    """FlashAttention forward fp16, Q, K, V ~ N(0, 1) (seed 3).  One step = the non-causal and
+    the causal kernel, each on its own buffer set."""
+
+    name = "FlashAttention fwd fp16 B=4 H=16 S=4096 D=128 (non-causal + causal)"
+    metric = "FlashAttention forward throughput (4*B*H*S^2*D flops, halved when causal)"
+    unit = "TFLOPS"
+    dtype = "f16 x f16 -> f32 accumulate, f32 softmax, f16 out"
+    bound = "tensor"
+    scaling = "weak"
+    shape = (4, 16, 4096, 128)
+    modes = (False, True)
+    shard_bh = False
+    seed = 3
+
+    def __init__(self, rank: int, world: int = 1):
+        import torch
+
+        from deca_b200.operators import FlashAttention
+
+        B, H, S, D = self.shape
+        if self.shard_bh:
+            assert (B * H) % world == 0
+            B, H = 1, B * H // world
+        self.B, self.H, self.S, self.D = B, H, S, D
+        g = torch.Generator(device="cpu").manual_seed(self.seed + 1000 * rank)
+        self.ops, self.dev = [], []
+        for causal in self.modes:
+            op = FlashAttention(B, H, S, S, D, causal=causal)
+            main = op.compile(op.build_mod(op.default_config()))["main"]
+            if not self.dev or not self.shard_bh:
+                q, k, v = (torch.randn(B, H, S, D, generator=g).half().cuda() for _ in range(3))
+            self.dev.append((q, k, v, torch.empty_like(q)))
+            self.ops.append((op, main))
+        q, k, v, o = self.dev[0]
+        self.host = tuple(t.cpu().pin_memory() for t in (q, k, v)) + (torch.empty_like(o, device="cpu").pin_memory(),)
+        self.units_per_step = sum(op.num_flops for op, _ in self.ops)
+        self.launches_per_step = len(self.ops)
+        cfg = self.ops[0][0].default_config()
+        self.dominant = ("fa_fwd", f"{'causal' if self.modes[0] else 'non-causal'} {cfg}")
+        self.dominant_units = self.ops[0][0].num_flops
+        self.traffic_key = f"fa_fwd_f16_{B}x{H}x{S}x{D}"
+        self.dominant_reps = 4
+        self.config = {"workload": self.name, "B_per_gpu": B, "H_per_gpu": H, "S": S, "D": D, "kernel_config": str(cfg),
+                       "l2": f"Q, K, V, O of one launch are {4 * B * H * S * D * 2 >> 20} MiB; launches alternate buffer sets"}
+
+    def step(self):
+        for (op, main), (q, k, v, o) in zip(self.ops, self.dev):
+            main(q, k, v, o)
+
+    def dominant_launch(self):
+        q, k, v, o = self.dev[0]
+        self.ops[0][1](q, k, v, o)
+
+    def step_e2e(self):
+        hq, hk, hv, ho = self.host
+        q, k, v, o = self.dev[0]
+        h2d = d2h = 0
+        for op, _ in self.ops:
+            for src, dst in ((hq, q), (hk, k), (hv, v)):
+                dst.copy_(src, non_blocking=True)
+                h2d += src.numel() * 2
+            op(q, k, v, out=o)
+            ho.copy_(o, non_blocking=True)
+            d2h += ho.numel() * 2
+        return h2d, d2h
+
+    def to_value(self, units_per_s):
+        return units_per_s / 1e12
+
+    roofline_value = to_value
+
+    def cpu_sample(self, target_s=12.0):
+        import numpy as np
+        import torch
+
+        import oracle
+
+        _, _, S, D = self.shape
+        g = torch.Generator(device="cpu").manual_seed(self.seed)
+        S_s = min(S, 2048)
+        q, k, v = (oracle.to_bits(torch.randn(1, 1, S_s, D, generator=g).numpy(), "float16") for _ in range(3))
+        causal_modes = self.modes
+
+        def once():
+            for causal in causal_modes:
+                oracle.attention(q, k, v, causal=causal)
+
+        once()
+        t0 = time.perf_counter()
+        once()
+        t1 = time.perf_counter() - t0
+        reps = max(1, int(target_s / max(t1, 1e-3)))
+        flops = sum(4 * S_s * S_s * D // (2 if c else 1) for c in causal_modes)
+        sample = f"{reps} x one head, S={S_s}, D={D}, modes causal={list(causal_modes)}"
+        return once, reps, flops, sample, np
+
+
+class AttentionShardedWorkload(AttentionWorkload):
+    """The multi-GPU attention configuration: B*H = 1024 heads split across the ranks (strong
+    scaling), causal, no collective."""
+
+    name = "FlashAttention fwd fp16 B=32 H=32 S=8192 D=128 causal split along B*H"
+    shape = (32, 32, 8192, 128)
+    modes = (True,)
+    shard_bh = True
+    scaling = "strong"
+    seed = 4
+
+
 def clock_summary_ok(c):
     bad = {"hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown"}
     return not (bad & set(c.get("reasons", [])))
@@ -239,7 +469,9 @@ def clock_summary_ok(c):
 def run_cpu_arm(wl, steps, warmup, as_reference_line, n_gpus):
     import oracle
 
-    once, reps, nbytes_once, sample, _ = wl.cpu_sample(target_s=12.0 if not as_reference_line else 4.0)
+    # reference arm: every step is a bounded sample, sized so that W + K steps take about 2 minutes
+    step_s = 12.0 if not as_reference_line else max(0.05, min(4.0, 120.0 / max(1, steps + warmup)))
+    once, reps, nbytes_once, sample, _ = wl.cpu_sample(target_s=step_s)
     if as_reference_line:
         for _ in range(warmup):
             once()
@@ -283,10 +515,10 @@ def main():
         if rank != 0:
             return
         wl = WORKLOADS[args.workload].__new__(WORKLOADS[args.workload])
-        base, per_step = run_cpu_arm(wl, max(1, min(args.steps, 3)), min(args.warmup, 1), True, world)
+        base, per_step = run_cpu_arm(wl, args.steps, args.warmup, True, world)
         line = {"impl": "reference", "metric": wl.metric, "value": base["value"], "unit": wl.unit, "n_gpus": args.gpus,
-                "steps": max(1, min(args.steps, 3)), "warmup": min(args.warmup, 1), "ms_per_step": per_step * 1e3,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
+                "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype,
                 "data": "synthetic", "config": {"workload": wl.name}, "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
@@ -309,7 +541,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    wl = WORKLOADS[args.workload](rank)
+    wl = WORKLOADS[args.workload](rank, world)
     peaks = measured_peaks()
 
     for _ in range(max(args.warmup, 3)):
@@ -395,17 +627,18 @@ def main():
         clocks = clk.summary()
         achieved = wl.roofline_value(wl.dominant_units / (dom_avg_ms / 1e3))
         if wl.bound == "hbm":
-            peak, punit = peaks["hbm_gbs"], "GB/s"
+            peak, punit, nominal = peaks["hbm_gbs"], "GB/s", 8000.0
         else:
-            peak, punit = peaks["bf16_tflops"], "TFLOP/s"
+            peak, punit, nominal = peaks["bf16_tflops"], "TFLOP/s", 2250.0
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config,
+            "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config,
             "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": L * args.steps, "launch_mode": "python" if args.no_graph else "cuda_graph",
             "roofline": {"bound": wl.bound, "kernel": f"{wl.dominant[0]} {wl.dominant[1]}", "achieved": achieved,
                          "peak": peak, "unit": punit, "frac": achieved / peak, "peak_source": peaks["source"],
+                         "nominal_peak": nominal, "frac_nominal": achieved / nominal,
                          "avg_launch_us": dom_avg_ms * 1e3, "traffic": NCU_TRAFFIC_BYTES.get(wl.traffic_key)},
             "clocks": clocks, "clocks_ok": clock_summary_ok(clocks),
         }
@@ -417,7 +650,8 @@ def main():
         dist.destroy_process_group()
 
 
-WORKLOADS = {"rowwise": RowwiseWorkload}
+WORKLOADS = {"rowwise": RowwiseWorkload, "gemm": GemmWorkload, "attention": AttentionWorkload,
+             "gemm_sharded": GemmShardedWorkload, "attention_sharded": AttentionShardedWorkload}
 
 if __name__ == "__main__":
     main()

@@ -1,0 +1,233 @@
+"""Analytic ranking of kernel configurations on B200.
+
+Same entry points as the reference's src/cost_model/CostModel.py -- ``gemm_tc_score`` (:207-271),
+``fa_score`` (:37-93), ``rowwise_score`` (:116-164) and the ``rank_*`` helpers (:96-99,
+:274-283) -- retargeted to the tcgen05 / TMA kernels: the tensor pipe is modelled by
+``arch.peak_tcgen05_flops``, operand traffic by the MMA's shared-memory reads and the TMA's
+L2 reads per flop, the epilogue by whether a second tensor-memory accumulator hides it, and
+the row-wise kernels by bytes in flight against Little's law.  Scores are "larger is better"
+and only meaningful relative to each other.
+"""
+
+import math
+
+from ..arch.Arch import Arch
+
+
+class CostModel:
+    def __init__(self):
+        pass
+
+    def cost(self, kernel, arch: Arch, compute_pattern):
+        pass
+
+
+# --------------------------------------------------------------------------------------- GEMM
+def gemm_tc_occupancy(cfg, arch: Arch):
+    """Resident CTAs per SM: the kernel is persistent with one CTA per SM."""
+    return 1
+
+
+def gemm_wave_dram_bytes_per_flop(cfg, arch: Arch, M: int, N: int, K: int, slots: int) -> float:
+    """DRAM bytes per flop of A / B for one wave of ``slots`` concurrent tiles walking the
+    output in groups of ``raster`` tile rows; operands that fit in half the L2 are fetched once."""
+    if (M * K + K * N) * 2 <= 0.5 * arch.l2_bytes:
+        return (M * K + K * N) * 2 / (2.0 * M * N * K)
+    GM, GN = -(-M // cfg.BM), -(-N // cfg.BN)
+    g = max(1, min(cfg.raster, GM))
+    cols = min(GN, math.ceil(slots / g))
+    rows = min(GM, g * math.ceil(slots / (g * GN)))
+    tiles = min(slots, GM * GN)
+    return (rows * cfg.BM + cols * cfg.BN) / (tiles * cfg.BM * cfg.BN)
+
+
+def gemm_tc_score(cfg, arch: Arch, M: int, N: int, K: int) -> float:
+    """Heuristic score of a tcgen05 GEMM config.
+
+    Per-SM time per flop of the main loop as a roofline whose terms overlap almost fully (TMA
+    and MMA are asynchronous to each other):
+    - tensor pipe at ``arch.peak_tcgen05_flops``
+    - shared memory: per 16-deep k step the MMAs read BM*32 bytes of A and, once per 128-row
+      half, BN*32 bytes of B, for 2*BM*BN*16 flops, against 128 B/clk
+    - L2 -> SM: (BM + BN) * 128 bytes per 64-deep K block for 2*BM*BN*64 flops
+    - DRAM: unique A / B bytes of one wave (grouped rasterisation)
+    Then wave quantisation of the persistent grid, ring depth against ~1 us of L2 latency,
+    the epilogue (hidden by a second accumulator, else serial), wasted columns of partial tiles.
+    """
+    sm = arch.sm_nums
+    halves = cfg.BM // 128
+    peak = arch.peak_tcgen05_flops * 1e9
+    t_mma = sm / peak
+    smem_bpf = (cfg.BM * 32 + halves * cfg.BN * 32) / (2.0 * cfg.BM * cfg.BN * 16)
+    t_smem = smem_bpf / arch.smem_bw_per_sm
+    l2_bpf = (cfg.BM + cfg.BN) / (cfg.BM * cfg.BN)
+    t_l2 = l2_bpf * sm / (arch.l2_bw * 1e9)
+    GM, GN = -(-M // cfg.BM), -(-N // cfg.BN)
+    tiles = GM * GN
+    slots = min(sm, tiles)
+    t_dram = gemm_wave_dram_bytes_per_flop(cfg, arch, M, N, K, slots) * sm / (arch.dram_bw * 1e9)
+    terms = sorted([t_mma, t_smem, t_l2, t_dram])
+    t_flop = terms[-1] + 0.1 * sum(terms[:-1])
+
+    waves = math.ceil(tiles / sm)
+    wave_eff = tiles / (waves * sm)
+    useful = (M * N) / (GM * cfg.BM * GN * cfg.BN)  # partial tiles compute zero-filled rows / columns
+
+    # bytes in flight per SM needed to cover ~1 us of L2 latency at the MMA's consumption rate
+    need = l2_bpf / t_mma * 1e-6
+    in_flight = (cfg.stages - 1) * (cfg.BM + cfg.BN) * 128
+    pipe = min(1.0, in_flight / need) ** 0.5
+    pipe *= 1.0 - getattr(arch, "gemm_excess_stage_penalty", 0.0) * max(0, cfg.stages - 1 - math.ceil(need / ((cfg.BM + cfg.BN) * 128)))
+
+    # epilogue: ~(BM/32 warps-rows) x (BN/64) panels of ~500 cycles per warp, 4 warps in parallel
+    tile_cycles = 2.0 * cfg.BM * cfg.BN * K / (peak / sm / arch.sm_clock_hz)
+    epi_cycles = (cfg.BM // 128) * (cfg.BN // 64) * (500 if cfg.epi_smem else 900)
+    epi = 1.0 if cfg.acc_bufs == 2 else tile_cycles / (tile_cycles + epi_cycles)
+    if cfg.acc_bufs == 2 and not cfg.epi_smem:
+        epi = 0.97
+
+    return wave_eff * useful * pipe * epi / (t_flop / t_mma)
+
+
+def rank_gemm_configs(configs, arch: Arch, M: int, N: int, K: int, top_n: int | None = None):
+    """Sort GEMM configs by ``gemm_tc_score`` (best first)."""
+    ranked = sorted(configs, key=lambda c: gemm_tc_score(c, arch, M, N, K), reverse=True)
+    return ranked[:top_n] if top_n else ranked
+
+
+# ---------------------------------------------------------------------------- FlashAttention
+def fa_occupancy(cfg, arch: Arch, D: int, grid: int):
+    """(resident CTAs per SM, occupancy): shared memory and tensor memory allow one CTA."""
+    from ..kernels.flash_attn_b200 import smem_bytes, tmem_columns
+
+    by_smem = (max(arch.shared_mem_config_options) * 1024) // (smem_bytes(cfg, D) + 1024)
+    by_tmem = getattr(arch, "tmem_columns", 512) // tmem_columns(cfg, D)
+    ctas = max(1, min(by_smem, by_tmem))
+    return ctas, ctas * cfg.threads / 32 / arch.max_resident_warps_per_sm
+
+
+def fa_score(cfg, arch: Arch, shape, causal: bool = False) -> float:
+    """Heuristic score of a FlashAttention config.
+
+    Per KV tile and 128-row Q tile the tensor pipe needs 4*128*Bc*D / flops-per-clk cycles; the
+    softmax warps need 128*Bc / 16 cycles of the exp2 unit (16 per clk per SM) plus about three
+    fp32 instructions per score over 128 lanes.  The MMA of the next score tile and the P V
+    product of the previous one overlap the softmax, so the tile time is the larger of the two
+    plus a hand-off (barrier round trips, tcgen05.ld latency).  Shared memory is a second
+    bound: both MMAs read both operands from it (Q and K, P and V) and P is written to it.
+    Causal: the diagonal tile is computed in full, so only the useful share of it counts; the
+    wave tail of the grid and the K/V ring depth (latency hiding) complete the model.
+    """
+    B, H, S_q, S_kv, D = shape
+    clk = arch.sm_clock_hz
+    fpc = arch.peak_tcgen05_flops * 1e9 / arch.sm_nums / clk  # flops per clock per SM
+    flops_tile = 4.0 * 128 * cfg.Bc * D
+    mma = flops_tile / fpc
+    # softmax: one warp per scheduler, so dependent-instruction latency shows; fitted to B200
+    # measurements at B4 H16 S4096 (about 0.20 clk per score at Bc = 64, 0.26 at Bc = 128)
+    softmax = 128.0 * cfg.Bc * (0.14 + 0.0009 * cfg.Bc)
+    # operand delivery: the K and V tiles of one step and the MMAs' shared-memory reads
+    operands = 16.0 * D * (cfg.Bc / 64.0)
+    handoff = 300.0
+    tile = max(mma, softmax, operands) + handoff
+    eff = mma / tile
+
+    n_q = S_q // cfg.Br
+    grid = n_q * B * H
+    ctas, _ = fa_occupancy(cfg, arch, D, grid)
+    slots = arch.sm_nums * ctas
+    wave_eff = grid / (math.ceil(grid / slots) * slots)
+    pipe = 1.0 if cfg.stages >= 2 else 0.93
+    pipe *= 1.0 - 0.01 * max(0, cfg.stages - 2)
+    useful = 1.0
+    if causal:
+        computed = sum(-(-(i + 1) * cfg.Br // cfg.Bc) * cfg.Bc for i in range(n_q)) * cfg.Br
+        useful = S_q * (S_q + 1) / 2 / computed
+    sync = 1.0 / (1.0 + getattr(arch, "fa_cta_sync_penalty", 0.0))
+    return eff * wave_eff * pipe * useful * sync
+
+
+def rank_fa_configs(configs, arch: Arch, shape, causal: bool = False, top_n: int | None = None):
+    """Sort FlashAttention configs by ``fa_score`` (best first)."""
+    ranked = sorted(configs, key=lambda c: fa_score(c, arch, shape, causal), reverse=True)
+    return ranked[:top_n] if top_n else ranked
+
+
+# ---------------------------------------------------------------------------------- row-wise
+def rowwise_occupancy(cfg, arch: Arch, op: str, N: int):
+    """Resident CTAs per SM of a row-wise config (the bulk-copy mode is one persistent CTA)."""
+    from ..kernels.rowwise_b200 import est_regs_per_thread
+
+    if cfg.mode == "tma":
+        return 1
+    regs = (min(255, est_regs_per_thread(cfg, N, op)) + 7) // 8 * 8
+    warps = cfg.threads // 32
+    ctas = min(arch.max_registers_per_sm // (regs * cfg.threads), arch.max_resident_warps_per_sm // warps,
+               arch.max_resident_blocks_per_sm)
+    return max(int(ctas), 1)
+
+
+def rowwise_score(cfg, arch: Arch, op: str, M: int, N: int, type_size: int = 2) -> float:
+    """Heuristic score of a memory-bound row-wise config.
+
+    - memory parallelism: bytes of loads in flight per SM against Little's law (DRAM bandwidth
+      per SM x ``arch.dram_latency_s``).  reg: every chunk of the row is requested up front by all
+      resident threads, but a CTA loads, reduces, then stores, so only part of the residents are
+      in their load phase; tma: rows_per_block * unroll whole rows are always in flight
+    - issue pressure: the arithmetic costs about 8 instructions per element (softmax) or 5
+      (RMSNorm); one persistent 512-thread CTA cannot issue them fast enough at full bandwidth,
+      many small resident CTAs can (measured: reg 128-thread CTAs reach 95 % of the copy
+      bandwidth at 16384 x 4096, the bulk-copy mode 70 %)
+    - block barriers couple the rows of a CTA: rows_per_block > 1 costs (measured -12 % per doubling)
+    - wave efficiency, twopass re-read (from L2 when the rows in flight fit), cross-warp
+      reductions, tail lanes, 8-byte accesses as in the reference's model
+    """
+    from ..kernels.rowwise_b200 import num_chunks
+
+    ctas = rowwise_occupancy(cfg, arch, op, N)
+    chunks = num_chunks(cfg, N)
+    need = arch.dram_bw * 1e9 / arch.sm_nums * getattr(arch, "dram_latency_s", 1e-6)
+    if cfg.mode == "tma":
+        in_flight = cfg.rows_per_block * cfg.unroll * N * type_size
+        phase = 1.0
+    else:
+        per_thread = (chunks if cfg.mode == "reg" else cfg.unroll) * cfg.vec * type_size
+        in_flight = ctas * cfg.threads * per_thread
+        phase = 1.0 - 0.35 / ctas if cfg.mode == "reg" else 1.0 - 0.1 / ctas
+    mem = min(1.0, in_flight / need)
+
+    # instruction issue: elements per clock per SM needed at full bandwidth vs what the resident
+    # warps can issue (4 schedulers; one CTA's phases serialise on its barriers)
+    inst_per_elem = 8.0 if op == "softmax" else 5.0
+    elems_per_clk = arch.dram_bw * 1e9 / arch.sm_nums / arch.sm_clock_hz / (2 * type_size)
+    warps = ctas * cfg.threads / 32
+    issue_capacity = 4.0 * min(1.0, warps / 24.0) * 32
+    issue = min(1.0, issue_capacity / (inst_per_elem * elems_per_clk * 2.2))
+
+    if cfg.mode == "tma":
+        grid_eff = 1.0
+        coupling = 0.9  # per-row barrier round trips of the single persistent CTA (measured)
+    else:
+        grid = M // cfg.rows_per_block
+        slots = arch.sm_nums * ctas
+        grid_eff = grid / (math.ceil(grid / slots) * slots)
+        coupling = 0.88 ** math.log2(cfg.rows_per_block) if cfg.threads > 128 else 1.0
+
+    passes = 1.0
+    if cfg.mode == "twopass":
+        footprint = arch.sm_nums * ctas * cfg.rows_per_block * N * type_size
+        hit = min(1.0, 0.6 * arch.l2_bytes / footprint)
+        passes = 1.0 + 0.5 * (hit * arch.dram_bw / arch.l2_bw + (1.0 - hit))
+
+    nw = cfg.threads_per_row // 32
+    reduce = 1.0 / (1.0 + 0.02 * math.log2(nw or 1) + (0.03 if nw > 1 else 0.0))
+    tail = N / (chunks * cfg.threads_per_row * cfg.vec) if cfg.mode != "twopass" else 1.0
+    lanes = 1.0 if cfg.vec * type_size >= 16 else 0.97
+    hint = 1.01 if cfg.hint else 1.0
+    return mem * phase * issue * grid_eff * coupling * reduce * (0.7 + 0.3 * tail) * lanes * hint / passes
+
+
+def rank_rowwise_configs(configs, arch: Arch, op: str, M: int, N: int, top_n: int | None = None):
+    """Sort row-wise configs by ``rowwise_score`` (best first)."""
+    ranked = sorted(configs, key=lambda c: rowwise_score(c, arch, op, M, N), reverse=True)
+    return ranked[:top_n] if top_n else ranked

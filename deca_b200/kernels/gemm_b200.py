@@ -93,12 +93,10 @@ def default_config(M: int, N: int, K: int) -> GemmConfig:
 
     if tiles(256, 256) >= sms:
         bm, bn, stages, acc = 256, 256, 3, 1
-    elif tiles(128, 256) >= sms:
+    elif N > 128:
         bm, bn, stages, acc = 128, 256, 4, 2
-    elif tiles(128, 128) >= sms or N <= 128:
-        bm, bn, stages, acc = 128, 128, 6, 2
     else:
-        bm, bn, stages, acc = 128, 256, 4, 2
+        bm, bn, stages, acc = 128, 128, 6, 2
     if N <= 64:
         bm, bn, stages, acc = 128, 64, 8, 2
     gm = -(-M // bm)
