@@ -56,8 +56,8 @@ def solve_gemm_tc(arch, M: int, N: int, K: int, type_size: int = 2, count: int =
     # shared memory: ring of A and B tiles, epilogue staging, barriers
     smem = st * (bm * 64 + 64 * bn) * type_size + If(epi == 1, BitVecVal(32768, 32), BitVecVal(0, 32)) + SMEM_RESERVED
     s.add(ULE(smem, arch.max_dyn_smem_per_block))
-    # a tile wider than the problem only wastes MMA columns
-    s.add(Or(ULE(bn, BitVecVal(max(N, 64), 32)), bn == 64))
+    # a tile at least twice as wide as the problem only wastes MMA columns
+    s.add(Or(ULE(bn, BitVecVal(max(2 * N - 1, 64), 32)), bn == 64))
 
     results = []
     gm_of = {128: -(-M // 128), 256: -(-M // 256)}

@@ -99,6 +99,7 @@ def default_config(M: int, N: int, K: int) -> GemmConfig:
         bm, bn, stages, acc = 128, 128, 6, 2
     if N <= 64:
         bm, bn, stages, acc = 128, 64, 8, 2
+    stages = max(2, min(stages, -(-K // 64)))  # no deeper than the number of K blocks
     gm = -(-M // bm)
     raster = 8
     while raster > 1 and gm < raster:

@@ -1,0 +1,122 @@
+"""CPU tests of the config search (Solver + cost model), the kernel-spec build flow in worker
+processes, and the log-record format of the CLIs."""
+
+import os
+import re
+
+import pytest
+
+
+@pytest.fixture(scope="module")
+def arch():
+    from deca_b200.arch.B200 import B200
+
+    return B200()
+
+
+def test_every_gemm_solution_is_valid_and_ranked(arch):
+    from deca_b200.cost_model.CostModel import gemm_tc_score, rank_gemm_configs
+    from deca_b200.kernels.gemm_b200 import check_config, default_config
+    from deca_b200.Solver import solve_gemm_tc
+
+    for shape in ((4096, 4096, 4096), (2048, 2048, 2048), (65536, 8192, 8192), (64, 80, 96), (300, 264, 328)):
+        cfgs = solve_gemm_tc(arch, *shape)
+        assert cfgs and len(set(cfgs)) == len(cfgs)
+        for c in cfgs:
+            check_config(c, *shape)
+            assert gemm_tc_score(c, arch, *shape) > 0
+        ranked = rank_gemm_configs(cfgs, arch, *shape, top_n=24)
+        assert len(ranked) == min(24, len(cfgs))
+        d = default_config(*shape)
+        assert d in cfgs
+    # large squares: the model's favourite is the tile shape measured best on B200
+    best = rank_gemm_configs(solve_gemm_tc(arch, 8192, 8192, 8192), arch, 8192, 8192, 8192)[0]
+    assert (best.BM, best.BN) == (256, 256)
+    assert solve_gemm_tc(arch, 4096, 4096, 4096, acc_f16=True) == []
+
+
+def test_every_attention_solution_is_valid(arch):
+    from deca_b200.cost_model.CostModel import rank_fa_configs
+    from deca_b200.kernels.flash_attn_b200 import check_config
+    from deca_b200.Solver import solve_flash_attn
+
+    for shape in ((4, 16, 4096, 4096, 128), (4, 16, 4096, 4096, 64), (1, 2, 128, 640, 128), (32, 32, 8192, 8192, 128)):
+        cfgs = solve_flash_attn(arch, *shape)
+        assert cfgs
+        for c in cfgs:
+            check_config(c, shape[2], shape[3], shape[4])
+        for causal in (False, True):
+            if causal and shape[2] != shape[3]:
+                continue
+            assert rank_fa_configs(cfgs, arch, shape, causal)[0] in cfgs
+    # measured on B200: 128-key tiles win at D = 128, 64-key tiles at D = 64
+    assert rank_fa_configs(solve_flash_attn(arch, 4, 16, 4096, 4096, 128), arch, (4, 16, 4096, 4096, 128))[0].Bc == 128
+    assert rank_fa_configs(solve_flash_attn(arch, 4, 16, 4096, 4096, 64), arch, (4, 16, 4096, 4096, 64))[0].Bc == 64
+
+
+def test_every_rowwise_solution_is_valid(arch):
+    from deca_b200.cost_model.CostModel import rank_rowwise_configs
+    from deca_b200.kernels.rowwise_b200 import check_config
+    from deca_b200.Solver import solve_rowwise
+
+    for op in ("softmax", "rmsnorm"):
+        for shape in ((16384, 4096), (4096, 1024), (1024, 128256), (3, 1000)):
+            cfgs = solve_rowwise(arch, op, *shape)
+            assert cfgs, (op, shape)
+            for c in cfgs:
+                check_config(c, op, *shape, "float16")
+            top = rank_rowwise_configs(cfgs, arch, op, *shape, top_n=3)
+            assert all(t in cfgs for t in top)
+    # measured on B200 at 16384 x 4096: register mode, 128 threads per row, one row per CTA
+    top = rank_rowwise_configs(solve_rowwise(arch, "softmax", 16384, 4096), arch, "softmax", 16384, 4096)[0]
+    assert (top.mode, top.threads_per_row, top.rows_per_block) == ("reg", 128, 1)
+    # rows that cannot live in registers fall back to the two-pass mode
+    assert all(c.mode == "twopass" for c in solve_rowwise(arch, "softmax", 1024, 1 << 20))
+
+
+def _crash(*args):
+    os._exit(3)
+
+
+def test_build_all_in_workers_and_serial_rebuild(tmp_path):
+    """Specs are written by spawned workers; a worker that dies breaks the pool and the affected
+    configs are rebuilt serially (the reference's behaviour, test_gemm_tc.py:88-97)."""
+    from deca_b200.cli import _tune
+    from deca_b200.kernels.gemm_b200 import GemmConfig, build_gemm_tc_to_file
+    from deca_b200.kernels.module import KernelSpec
+
+    cfgs = [GemmConfig(BN=bn, stages=st) for bn in (128, 256) for st in (3, 4)]
+    paths = _tune.build_all(build_gemm_tc_to_file, lambda c, p: ((1024, 1024, 1024), c, "sm_100a", p), cfgs, 2, "t_")
+    assert set(paths) == set(cfgs)
+    for c, p in paths.items():
+        spec = KernelSpec.from_json(open(p).read())
+        assert spec.family == "gemm" and GemmConfig(**spec.config) == c
+    # invalid configs are reported and skipped, valid ones still come back
+    bad = GemmConfig(BN=96)
+    out = _tune.build_all(build_gemm_tc_to_file, lambda c, p: ((1024, 1024, 1024), c, "sm_100a", p), [bad, cfgs[0]], 2, "t_")
+    assert set(out) == {cfgs[0]}
+
+
+def test_log_record_format(tmp_path, monkeypatch):
+    from deca_b200.cli import _tune
+
+    monkeypatch.setenv("DECA_LOG_DIR", str(tmp_path))
+    assert _tune.log_path() == str(tmp_path / "deca_performance.log")
+    msg = (f"{_tune.stamp()} [NVIDIA B200]\n DeCA GEMMTC(M=4096, N=4096, K=4096, float16), config: X (cost-model rank 1/24)\n"
+           f" throughput: 1386.5 TFLOPS (62% of fp32-acc TC peak), runtime: 0.0989 ms, max err: 3.12e-02\n"
+           f" torch: 1427.1 TFLOPS, runtime: 0.0963 ms, ratio: 0.974\n compile time: 0.3 s, total tuning time: 9.1 s\n")
+    with open(_tune.log_path(), "a") as log:
+        _tune.emit(msg, log)
+    text = open(_tune.log_path()).read()
+    assert re.match(r"\d{4}-\d\d-\d\d \d\d:\d\d:\d\d \[NVIDIA B200\]\n DeCA GEMMTC\(", text)
+    assert text.endswith("\n\n")
+    # flags of the three CLIs
+    from deca_b200.cli import test_flash_attn, test_gemm_tc, test_rowwise
+
+    a = test_gemm_tc.parse_args([])
+    assert (a.shape, a.top_n, a.finalists, a.rounds, a.sweep) == ([4096, 4096, 4096], 24, 3, 5, False)
+    a = test_flash_attn.parse_args(["--causal"])
+    assert (a.shape, a.top_n, a.causal) == ([4, 16, 4096, 128], 16, True)
+    assert test_flash_attn.parse_shape([4, 16, 4096, 128]) == (4, 16, 4096, 4096, 128)
+    a = test_rowwise.parse_args(["--op", "rmsnorm", "--dtype", "bf16"])
+    assert (a.shape, a.op, a.dtype, a.eps, a.top_n) == ([16384, 4096], "rmsnorm", "bf16", 1e-6, 24)
