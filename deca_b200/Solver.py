@@ -81,21 +81,26 @@ def solve_flash_attn(arch, B: int, H: int, S_q: int, S_kv: int, D: int, type_siz
     from .kernels.flash_attn_b200 import FAConfig, check_config
 
     s = Solver()
-    bc, st = BitVecs("bc st", 32)
+    bc, st, qt, pt = BitVecs("bc st qt pt", 32)
     s.add(Or(bc == 64, bc == 128))
-    s.add(And(UGE(st, 1), ULE(st, 4)))
+    s.add(Or(qt == 1, qt == 2))
+    s.add(ULE(pt, 1), Implies(qt == 1, pt == 0))
     s.add(URem(BitVecVal(S_kv, 32), bc) == 0)
-    # do not pipeline deeper than the number of KV tiles
-    s.add(ULE(st, UDiv(BitVecVal(S_kv, 32), bc)))
-    # shared memory: Q tile + K and V rings + double-buffered P + barriers
-    smem = (128 * D + 2 * st * bc * D + 2 * 128 * bc) * type_size + 2048
-    s.add(ULE(smem, arch.max_dyn_smem_per_block))
-    # tensor memory: two score buffers + the output accumulator
-    s.add(ULE(2 * bc + D, getattr(arch, "tmem_columns", 512)))
+    s.add(URem(BitVecVal(S_q, 32), 128 * qt) == 0)
+    n_kv = UDiv(BitVecVal(S_kv, 32), bc)
+    # one Q tile per CTA: a K ring and a V ring of `st` slots, double-buffered P, two score buffers
+    smem1 = (128 * D + 2 * st * bc * D + 2 * 128 * bc) * type_size + 2048
+    s.add(Implies(qt == 1, And(UGE(st, 1), ULE(st, 4), ULE(st, n_kv), ULE(smem1, arch.max_dyn_smem_per_block),
+                               ULE(2 * bc + D, getattr(arch, "tmem_columns", 512)))))
+    # two Q tiles per CTA: one ring of `st` slots shared by K and V tiles, one P and one score buffer per tile
+    smem2 = (2 * 128 * D + st * bc * D + If(pt == 1, BitVecVal(0, 32), BitVecVal(2 * 128, 32) * bc)) * type_size + 2048
+    s.add(Implies(qt == 2, And(bc == 128, UGE(st, 2), ULE(st, 8), ULE(st, 2 * n_kv),
+                               ULE(smem2, arch.max_dyn_smem_per_block),
+                               ULE(2 * bc + 2 * D, getattr(arch, "tmem_columns", 512)))))
 
     results = []
-    for vals in _all_models(s, (bc, st), count):
-        cfg = FAConfig(Br=128, Bc=vals[0], stages=vals[1], q_tiles=1)
+    for vals in _all_models(s, (bc, st, qt, pt), count):
+        cfg = FAConfig(Br=128, Bc=vals[0], stages=vals[1], q_tiles=vals[2], p_tmem=bool(vals[3]))
         try:
             check_config(cfg, S_q, S_kv, D)
         except AssertionError:

@@ -1,0 +1,405 @@
+// FlashAttention forward for B200, two Q tiles per CTA (FAConfig q_tiles = 2, Bc = 128).
+//
+// Same arithmetic as fa_fwd_f16.cu; what changes is the schedule.  A CTA owns two consecutive
+// 128-row Q tiles of one head (group A = even tile, group B = odd tile) and 320 threads:
+//   warp 0      TMA producer: both Q tiles once, then K_0, V_0, K_1, V_1, ... through ONE ring of
+//               `stages` slots; every K / V tile is loaded once and used by both groups.
+//   warp 1      MMA issuer.  Tensor memory holds S_A, S_B (128 columns each) and O_A, O_B (D columns
+//               each).  Issue order per KV step j: when P_A(j) is ready, S_A(j+1) = Q_A K_{j+1}^T
+//               then O_A += P_A(j) V_j; then the same for B.  The MMAs of one group run while the
+//               other group is in its softmax.
+//   warps 2-5   softmax + epilogue of group A, warps 6-9 of group B: one thread per query row, two
+//               softmax warps per scheduler.
+// Causal: the pair (2t, 2t+1) visits KV tiles 0..2t+1; group A stops one tile earlier; each
+// group masks its own diagonal tile; pairs are scheduled longest first.
+// All mbarrier waits are bounded (ptx.cuh); a wait that runs out raises the CTA's abort flag and
+// every role falls through to the common teardown.
+#include <atomic>
+#include <type_traits>
+
+#include "fa_softmax.cuh"
+#include "ptx.cuh"
+#include "tmap.cuh"
+
+namespace deca {
+namespace {
+
+constexpr int kBr = 128;
+constexpr int kBc = 128;
+constexpr int kThreads2 = 320;
+
+struct Fa2Args {
+    int S_q, S_kv;
+    int causal;
+    int stages;  // K/V ring slots
+    float sl2;
+    DeviceStatus *status;
+};
+
+// PTMEM: P lives in tensor memory (aliasing the first 64 columns of its score tile) and is the
+// A operand of the P V product, so neither the P write nor the P read touches shared memory and
+// the K/V ring gets the space; the product of step j must then be issued BEFORE the next score
+// MMA of the same group overwrites that tile.
+template <int D, bool PTMEM>
+__global__ void __launch_bounds__(kThreads2, 1)
+fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const Fa2Args g) {
+    using P16 = Pack16<DECA_F16>;
+    constexpr uint32_t kQBytes = kBr * D * 2;
+    constexpr uint32_t kKVBytes = kBc * D * 2;
+    constexpr uint32_t kPBytes = kBr * kBc * 2;
+    constexpr uint32_t kKVBlock = kBc * 128;
+    constexpr uint32_t kIdescQK = make_idesc_f16(DECA_F16, false, false, kBr, kBc);
+    constexpr uint32_t kIdescPV = make_idesc_f16(DECA_F16, false, true, kBr, D);
+    constexpr uint32_t kTmemCols = 512;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (base - raw);
+
+    const int stages = g.stages;
+    const uint32_t sQ = base;                   // Q_A, Q_B
+    const uint32_t sP = sQ + 2 * kQBytes;       // P_A, P_B (unless P is in tensor memory)
+    const uint32_t sKV = sP + (PTMEM ? 0u : 2 * kPBytes);  // ring
+    const uint32_t sBar = sKV + stages * kKVBytes;
+    const uint32_t q_full = sBar;
+    auto kv_full = [&](int i) { return sBar + 8u * (1 + i); };
+    auto kv_empty = [&](int i) { return sBar + 8u * (1 + stages + i); };
+    const uint32_t fixed0 = sBar + 8u * (1 + 2 * stages);
+    auto s_full = [&](int grp) { return fixed0 + 8u * grp; };
+    auto p_full = [&](int grp) { return fixed0 + 8u * (2 + grp); };
+    auto pv_done = [&](int grp) { return fixed0 + 8u * (4 + grp); };
+    const uint32_t drain_bar = fixed0 + 8u * 6;
+    const uint32_t slot_addr = fixed0 + 8u * 7;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + (slot_addr - base));
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int n_pairs = g.S_q / (2 * kBr);
+    const int pair = g.causal ? (n_pairs - 1 - (int)blockIdx.x) : (int)blockIdx.x;
+    const int bh = blockIdx.y;
+    const int q_row0 = bh * g.S_q + pair * 2 * kBr;  // first row of tile A in the [B*H*S_q, D] view
+    const int kv_row0 = bh * g.S_kv;
+    // KV tiles visited by group A / B (B always visits at least as many as A)
+    const int n_a = g.causal ? 2 * pair + 1 : g.S_kv / kBc;
+    const int n_b = g.causal ? 2 * pair + 2 : g.S_kv / kBc;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(q_full, 1);
+        for (int i = 0; i < stages; ++i) {
+            mbar_init(kv_full(i), 1);
+            mbar_init(kv_empty(i), 1);
+        }
+        for (int grp = 0; grp < 2; ++grp) {
+            mbar_init(s_full(grp), 1);
+            mbar_init(p_full(grp), 4);
+            mbar_init(pv_done(grp), 1);
+        }
+        mbar_init(drain_bar, 1);
+        fence_barrier_init();
+        prefetch_tensormap(&tmQ);
+        prefetch_tensormap(&tmK);
+        prefetch_tensormap(&tmV);
+        prefetch_tensormap(&tmO);
+    }
+    if (warp == 1) {
+        tmem_alloc(slot_addr, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    auto tS = [&](int grp) { return tmem_base + (uint32_t)(grp * kBc); };
+    auto tO = [&](int grp) { return tmem_base + 2u * kBc + (uint32_t)(grp * D); };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            bool ok = true;
+            mbar_arrive_expect_tx(q_full, 2 * kQBytes);
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+#pragma unroll
+                for (int blk = 0; blk < D / 64; ++blk)
+                    tma_load_2d(sQ + t * kQBytes + blk * 16384, &tmQ, blk * 64, q_row0 + t * kBr, q_full);
+            int s = 0;
+            uint32_t ph = 0;
+            int n_items = 0;
+            for (int i = 0; i < 2 * n_b; ++i) {  // item 2j = K_j, 2j + 1 = V_j
+                if (!mbar_wait(kv_empty(s), ph ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                const int row = kv_row0 + (i >> 1) * kBc;
+                const CUtensorMap *tm = (i & 1) ? &tmV : &tmK;
+                mbar_arrive_expect_tx(kv_full(s), kKVBytes);
+#pragma unroll
+                for (int blk = 0; blk < D / 64; ++blk)
+                    tma_load_2d(sKV + s * kKVBytes + blk * kKVBlock, tm, blk * 64, row, kv_full(s));
+                ++n_items;
+                if (++s == stages) s = 0, ph ^= 1u;
+            }
+            if (!ok) {
+                if (*abort_flag == 0) {
+                    *abort_flag = 1;
+                    report_timeout(g.status, 0x401u);
+                }
+                __shared__ uint32_t no_abort;
+                no_abort = 0;
+                (void)mbar_wait(q_full, 0, &no_abort);
+                for (int st = 0; st < stages; ++st) {
+                    const int n_st = (n_items + stages - 1 - st) / stages;
+                    if (n_st > 0) (void)mbar_wait(kv_full(st), (uint32_t)((n_st - 1) & 1), &no_abort);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            bool ok = true;
+            // ring slot / parity of item i
+            auto slot_of = [&](int i) { return i % stages; };
+            auto par_of = [&](int i) { return (uint32_t)((i / stages) & 1); };
+            auto issue_qk = [&](int grp, int j) {  // S_grp = Q_grp K_j^T
+                const uint32_t kb = sKV + slot_of(2 * j) * kKVBytes;
+                const uint32_t qb = sQ + grp * kQBytes;
+#pragma unroll
+                for (int kd = 0; kd < D / 16; ++kd) {
+                    const uint64_t adesc = make_smem_desc(qb + (kd / 4) * 16384 + (kd % 4) * 32, 16, 1024);
+                    const uint64_t bdesc = make_smem_desc(kb + (kd / 4) * kKVBlock + (kd % 4) * 32, 16, 1024);
+                    umma_f16_ss(tS(grp), adesc, bdesc, kIdescQK, kd != 0 ? 1u : 0u);
+                }
+                umma_commit(s_full(grp));
+            };
+            auto issue_pv = [&](int grp, int j) {  // O_grp (+)= P_grp V_j
+                const uint32_t pb = sP + grp * kPBytes;
+                const uint32_t vb = sKV + slot_of(2 * j + 1) * kKVBytes;
+#pragma unroll
+                for (int kk = 0; kk < kBc / 16; ++kk) {
+                    const uint64_t bdesc = make_smem_desc(vb + kk * 2048, kKVBlock, 1024);
+                    if constexpr (PTMEM) {
+                        // 16 keys = 8 packed columns of the P tile in tensor memory
+                        umma_f16_ts(tO(grp), tS(grp) + kk * 8, bdesc, kIdescPV, (j | kk) != 0 ? 1u : 0u);
+                    } else {
+                        const uint64_t adesc = make_smem_desc(pb + (kk / 4) * 16384 + (kk % 4) * 32, 16, 1024);
+                        umma_f16_ss(tO(grp), adesc, bdesc, kIdescPV, (j | kk) != 0 ? 1u : 0u);
+                    }
+                }
+                umma_commit(pv_done(grp));
+            };
+            ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(kv_full(slot_of(0)), par_of(0), abort_flag);
+            if (ok) {
+                tc_fence_after_sync();
+                issue_qk(0, 0);
+                issue_qk(1, 0);
+                umma_commit(kv_empty(slot_of(0)));
+            }
+            for (int j = 0; j < n_b && ok; ++j) {
+                // K_{j+1} (if any) and V_j must have landed
+                if (j + 1 < n_b && !mbar_wait(kv_full(slot_of(2 * j + 2)), par_of(2 * j + 2), abort_flag)) ok = false;
+                if (ok && !mbar_wait(kv_full(slot_of(2 * j + 1)), par_of(2 * j + 1), abort_flag)) ok = false;
+                if (!ok) break;
+                // group A: once P_A(j) is ready S_A is free as well
+                if (j < n_a) {
+                    if (!mbar_wait(p_full(0), (uint32_t)(j & 1), abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    if constexpr (PTMEM) {
+                        issue_pv(0, j);
+                        if (j + 1 < n_a) issue_qk(0, j + 1);
+                    } else {
+                        if (j + 1 < n_a) issue_qk(0, j + 1);
+                        issue_pv(0, j);
+                    }
+                }
+                // group B (always the last user of K_{j+1} and V_j)
+                if (!mbar_wait(p_full(1), (uint32_t)(j & 1), abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                if constexpr (PTMEM) {
+                    issue_pv(1, j);
+                    umma_commit(kv_empty(slot_of(2 * j + 1)));
+                    if (j + 1 < n_b) {
+                        issue_qk(1, j + 1);
+                        umma_commit(kv_empty(slot_of(2 * j + 2)));
+                    }
+                } else {
+                    if (j + 1 < n_b) {
+                        issue_qk(1, j + 1);
+                        umma_commit(kv_empty(slot_of(2 * j + 2)));
+                    }
+                    issue_pv(1, j);
+                    umma_commit(kv_empty(slot_of(2 * j + 1)));
+                }
+            }
+            if (!ok) {
+                if (*abort_flag == 0) {
+                    *abort_flag = 1;
+                    report_timeout(g.status, 0x402u);
+                }
+                __shared__ uint32_t no_abort2;
+                no_abort2 = 0;
+                umma_commit(drain_bar);
+                (void)mbar_wait(drain_bar, 0, &no_abort2);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ softmax + epilogue
+        const int grp = (warp - 2) >> 2;  // 0 = tile A, 1 = tile B
+        const int q = warp & 3;           // tensor-memory lane quarter
+        const int r = q * 32 + lane;
+        const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+        const int qt = 2 * pair + grp;
+        const int row_abs = qt * kBr + r;
+        const int n_kv = grp == 0 ? n_a : n_b;
+        const uint32_t tSg = tS(grp) + lane_off;
+        const uint32_t tOg = tO(grp) + lane_off;
+        const uint32_t pb = PTMEM ? tSg : sP + grp * kPBytes;
+        const float sl2 = g.sl2;
+        float m = kNegInf, l = 0.f;
+        bool ok = true;
+        auto wait_all = [&](uint32_t bar, uint32_t parity) {
+            return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag)) != 0;
+        };
+
+        for (int j = 0; j < n_kv; ++j) {
+            if (!wait_all(s_full(grp), (uint32_t)(j & 1))) {
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            const bool diag = g.causal && ((j + 1) * kBc - 1 > qt * kBr);
+            const int col0 = j * kBc;
+
+            // P (single buffer per group) was last read by the product of tile j - 1, which is also
+            // the product that completes O for a rescale
+            auto wait_prev = [&]() { return j == 0 || wait_all(pv_done(grp), (uint32_t)((j - 1) & 1)); };
+            const bool step_ok = diag ? fa_softmax_step<kBc, D, true, PTMEM>(tSg, tOg, pb, r, col0, row_abs, sl2, j == 0,
+                                                                             m, l, wait_prev, wait_prev)
+                                      : fa_softmax_step<kBc, D, false, PTMEM>(tSg, tOg, pb, r, col0, row_abs, sl2, j == 0,
+                                                                              m, l, wait_prev, wait_prev);
+            if (!step_ok) {
+                ok = false;
+                break;
+            }
+            // S is consumed, P (and a possibly rescaled O) are ready
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full(grp));
+        }
+
+        if (ok) ok = wait_all(pv_done(grp), (uint32_t)((n_kv - 1) & 1));
+        if (!ok) {
+            if (lane == 0 && *abort_flag == 0) {
+                *abort_flag = 1;
+                report_timeout(g.status, 0x403u);
+            }
+        } else {
+            // ---- epilogue: O / l -> fp16 -> shared (this group's Q tile space) -> TMA store
+            tc_fence_after_sync();
+            const float inv = 1.0f / l;
+            const uint32_t stage0 = sQ + grp * kQBytes;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tOg + c * 32, v);
+                tmem_ld_wait();
+                const uint32_t rowb = stage0 + (c / 2) * 16384 + q * 4096 + lane * 128;
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    const int chunk = (c & 1) * 4 + cc;
+                    const uint32_t dst = rowb + ((chunk ^ (lane & 7)) << 4);
+                    uint32_t o[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        o[i] = P16::pack(__uint_as_float(v[cc * 8 + 2 * i]) * inv,
+                                         __uint_as_float(v[cc * 8 + 2 * i + 1]) * inv);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                                 "r"(o[3])
+                                 : "memory");
+                }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+#pragma unroll
+                for (int blk = 0; blk < D / 64; ++blk)
+                    tma_store_2d(&tmO, stage0 + blk * 16384 + q * 4096, blk * 64, q_row0 + grp * kBr + q * 32);
+                tma_store_commit();
+                tma_store_wait<0>();
+            }
+        }
+        __syncwarp();
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+template <int D, bool PTMEM>
+int launch_fa2(const CUtensorMap &tmQ, const CUtensorMap &tmK, const CUtensorMap &tmV, const CUtensorMap &tmO,
+               const Fa2Args &g, dim3 grid, size_t smem, cudaStream_t st) {
+    static std::atomic<size_t> configured{0};
+    if (configured.load(std::memory_order_relaxed) < smem) {
+        cudaError_t e = cudaFuncSetAttribute(fa_fwd2_kernel<D, PTMEM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured.store(smem, std::memory_order_relaxed);
+    }
+    fa_fwd2_kernel<D, PTMEM><<<grid, kThreads2, smem, st>>>(tmQ, tmK, tmV, tmO, g);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+size_t fa2_smem_bytes(int D, int stages, bool ptmem) {
+    return 1024 + 2 * (size_t)kBr * D * 2 + (ptmem ? 0 : 2 * (size_t)kBr * kBc * 2) + (size_t)stages * kBc * D * 2 +
+           8 * (2 * (size_t)stages + 16);
+}
+
+// Host rules of the two-tile schedule; shared with deca_fa_fwd_f16_check_config.
+int fa2_check(int S_q, int S_kv, int D, const deca_fa_cfg &c) {
+    if (c.Bc != kBc || c.Br != kBr) return DECA_ERR_CONFIG;
+    if (S_q % (2 * kBr) != 0 || S_kv % kBc != 0) return DECA_ERR_CONFIG;
+    if (c.stages < 2 || c.stages > 8) return DECA_ERR_CONFIG;
+    if (fa2_smem_bytes(D, c.stages, c.p_tmem != 0) > 232448) return DECA_ERR_CONFIG;
+    return DECA_OK;
+}
+
+int fa2_launch(const CUtensorMap &tmQ, const CUtensorMap &tmK, const CUtensorMap &tmV, const CUtensorMap &tmO, int B,
+               int H, int S_q, int S_kv, int D, float softmax_scale, int causal, const deca_fa_cfg &c,
+               cudaStream_t st) {
+    Fa2Args g;
+    g.S_q = S_q, g.S_kv = S_kv;
+    g.causal = causal ? 1 : 0;
+    g.stages = c.stages;
+    g.sl2 = softmax_scale * kLog2e;
+    g.status = device_status_ptr();
+    if (!g.status) return (int)cudaErrorUnknown;
+    const dim3 grid((unsigned)(S_q / (2 * kBr)), (unsigned)(B * H), 1);
+    const bool ptmem = c.p_tmem != 0;
+    const size_t smem = fa2_smem_bytes(D, c.stages, ptmem);
+    if (ptmem)
+        return D == 128 ? launch_fa2<128, true>(tmQ, tmK, tmV, tmO, g, grid, smem, st)
+                        : launch_fa2<64, true>(tmQ, tmK, tmV, tmO, g, grid, smem, st);
+    return D == 128 ? launch_fa2<128, false>(tmQ, tmK, tmV, tmO, g, grid, smem, st)
+                    : launch_fa2<64, false>(tmQ, tmK, tmV, tmO, g, grid, smem, st);
+}
+
+}  // namespace deca

@@ -1,0 +1,211 @@
+// Per-row online softmax of one 128 x BC score tile held in tensor memory; shared by the two
+// FlashAttention schedules.  One thread owns one query row (one tensor-memory lane).
+//
+// Recurrence of the reference kernel (flash_attn_tir.py:403-438: finite -1e30 mask value, scale
+// folded into the exp2 argument, fp32 sum of the unrounded probabilities, P rounded to fp16) with
+// a lazily updated running max: as long as the tile's row max exceeds the running max m by at
+// most 2^8 in the exponent, m is kept (P <= 256 is exact enough in fp16 and everything is
+// normalised by l at the end), so the common case is ONE pass over the scores: exponentials with
+// the old max, the row sum and the tile max together.  Only when some row of the warp grew by
+// more (always on the first tile) the slow path runs: raise m, rescale l and the O accumulator in
+// tensor memory, and redo the exponentials with the new max.
+#pragma once
+
+#include <type_traits>
+
+#include "ptx.cuh"
+
+namespace deca {
+
+constexpr float kFaRescaleThreshold = 8.0f;  // log2 units
+
+// Exponentials of the row with max term `ms` (= m * sl2): writes P (fp16) into the K-major,
+// 128-byte swizzled shared tile at `p_base` (64-key blocks of 128 rows x 128 bytes) and returns
+// the row sum; with TRACK also folds the (masked) raw scores into `mx`.
+// With PTMEM the fp16 P tile goes to tensor memory instead, packed two keys per 32-bit column
+// into the first BC / 2 columns of the score tile it was computed from (`p_base` is then that
+// tile's tensor-memory address): the 64 scores of a chunk are in registers before the 32 columns
+// that receive their probabilities are overwritten, and no other thread touches this lane.
+template <int BC, bool MASKED, bool TRACK, bool PTMEM>
+__device__ __forceinline__ float fa_exp_tile(uint32_t tS, uint32_t p_base, int r, int col0, int row_abs, float sl2,
+                                             float ms, float &mx) {
+    using P16 = Pack16<DECA_F16>;
+    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+    float max4[4] = {kNegInf, kNegInf, kNegInf, kNegInf};
+#pragma unroll 1
+    for (int h = 0; h < BC / 64; ++h) {
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32b_x32(tS + h * 64, v0);
+        tmem_ld_32x32b_x32(tS + h * 64 + 32, v1);
+        tmem_ld_wait();
+        uint32_t p[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float s0 = __uint_as_float(v0[2 * i]), s1 = __uint_as_float(v0[2 * i + 1]);
+            float s2 = __uint_as_float(v1[2 * i]), s3 = __uint_as_float(v1[2 * i + 1]);
+            if constexpr (MASKED) {
+                const int cb = col0 + h * 64 + 2 * i;
+                if (cb > row_abs) s0 = kNegInf;
+                if (cb + 1 > row_abs) s1 = kNegInf;
+                if (cb + 32 > row_abs) s2 = kNegInf;
+                if (cb + 33 > row_abs) s3 = kNegInf;
+            }
+            if constexpr (TRACK) {
+                max4[0] = fmaxf(max4[0], s0), max4[1] = fmaxf(max4[1], s1);
+                max4[2] = fmaxf(max4[2], s2), max4[3] = fmaxf(max4[3], s3);
+            }
+            const float p0 = ex2_approx(fmaf(s0, sl2, -ms)), p1 = ex2_approx(fmaf(s1, sl2, -ms));
+            const float p2 = ex2_approx(fmaf(s2, sl2, -ms)), p3 = ex2_approx(fmaf(s3, sl2, -ms));
+            sum4[0] += p0, sum4[1] += p1, sum4[2] += p2, sum4[3] += p3;
+            p[i] = P16::pack(p0, p1);
+            p[16 + i] = P16::pack(p2, p3);
+        }
+        if constexpr (PTMEM) {
+            // p[i] holds keys (2i, 2i+1) of the first 32 and p[16 + i] of the second 32: 32 columns
+            tmem_st_32x32b_x32(p_base + h * 32, p);
+        } else {
+            const uint32_t rowb = p_base + h * 16384 + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint32_t dst = rowb + ((c ^ (r & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(p[4 * c]), "r"(p[4 * c + 1]),
+                             "r"(p[4 * c + 2]), "r"(p[4 * c + 3])
+                             : "memory");
+            }
+        }
+    }
+    if constexpr (PTMEM) tmem_st_wait();
+    if constexpr (TRACK) mx = fmaxf(fmaxf(max4[0], max4[1]), fmaxf(max4[2], max4[3]));
+    return (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+}
+
+// Fast-path variant for P in tensor memory: the exponentials (with the running max) are packed
+// into registers `pk` and NOT stored, because storing would overwrite the scores that a redo with
+// a raised max still needs; the caller stores them once the warp has voted that no row grew by
+// more than the threshold.  Also folds the (masked) raw scores into `mx`.
+template <int BC, bool MASKED>
+__device__ __forceinline__ float fa_exp_tile_hold(uint32_t tS, int col0, int row_abs, float sl2, float ms, float &mx,
+                                                  uint32_t (&pk)[BC / 2]) {
+    using P16 = Pack16<DECA_F16>;
+    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+    float max4[4] = {kNegInf, kNegInf, kNegInf, kNegInf};
+#pragma unroll
+    for (int h = 0; h < BC / 64; ++h) {
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32b_x32(tS + h * 64, v0);
+        tmem_ld_32x32b_x32(tS + h * 64 + 32, v1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float s0 = __uint_as_float(v0[2 * i]), s1 = __uint_as_float(v0[2 * i + 1]);
+            float s2 = __uint_as_float(v1[2 * i]), s3 = __uint_as_float(v1[2 * i + 1]);
+            if constexpr (MASKED) {
+                const int cb = col0 + h * 64 + 2 * i;
+                if (cb > row_abs) s0 = kNegInf;
+                if (cb + 1 > row_abs) s1 = kNegInf;
+                if (cb + 32 > row_abs) s2 = kNegInf;
+                if (cb + 33 > row_abs) s3 = kNegInf;
+            }
+            max4[0] = fmaxf(max4[0], s0), max4[1] = fmaxf(max4[1], s1);
+            max4[2] = fmaxf(max4[2], s2), max4[3] = fmaxf(max4[3], s3);
+            const float p0 = ex2_approx(fmaf(s0, sl2, -ms)), p1 = ex2_approx(fmaf(s1, sl2, -ms));
+            const float p2 = ex2_approx(fmaf(s2, sl2, -ms)), p3 = ex2_approx(fmaf(s3, sl2, -ms));
+            sum4[0] += p0, sum4[1] += p1, sum4[2] += p2, sum4[3] += p3;
+            pk[h * 32 + i] = P16::pack(p0, p1);
+            pk[h * 32 + 16 + i] = P16::pack(p2, p3);
+        }
+    }
+    mx = fmaxf(fmaxf(max4[0], max4[1]), fmaxf(max4[2], max4[3]));
+    return (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+}
+
+// (masked) row maximum of the tile
+template <int BC, bool MASKED>
+__device__ __forceinline__ float fa_row_max(uint32_t tS, int col0, int row_abs) {
+    float mx = kNegInf;
+#pragma unroll 1
+    for (int c = 0; c < BC / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tS + c * 32, v);
+        tmem_ld_wait();
+        float part[4] = {kNegInf, kNegInf, kNegInf, kNegInf};
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            float s = __uint_as_float(v[i]);
+            if constexpr (MASKED) {
+                if (col0 + c * 32 + i > row_abs) s = kNegInf;
+            }
+            part[i & 3] = fmaxf(part[i & 3], s);
+        }
+        mx = fmaxf(mx, fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])));
+    }
+    return mx;
+}
+
+// One KV step of the online softmax for this thread's row.  `tS` / `tO` are the tensor-memory
+// addresses of the score tile and of the O accumulator including the warp's lane offset.
+// `wait_p_free()` must return once the P tile at `p_base` may be overwritten, `wait_o_ready()`
+// once O holds the sum over all previous KV tiles (both return false when a bounded wait ran
+// out, and must be warp-uniform).  Updates m and l; returns false on such a failure.
+template <int BC, int D, bool MASKED, bool PTMEM, typename WaitP, typename WaitO>
+__device__ __forceinline__ bool fa_softmax_step(uint32_t tS, uint32_t tO, uint32_t p_base, int r, int col0, int row_abs,
+                                                float sl2, bool first_tile, float &m, float &l, WaitP wait_p_free,
+                                                WaitO wait_o_ready) {
+    if (!wait_p_free()) return false;
+    float mx, lsum = 0.f;
+    bool have_p = false;
+    if (first_tile) {
+        mx = fa_row_max<BC, MASKED>(tS, col0, row_abs);
+    } else if constexpr (PTMEM) {
+        // fast path, P to tensor memory: hold the packed probabilities until the vote, because
+        // storing them overwrites the scores a redo would need
+        uint32_t pk[BC / 2];
+        lsum = fa_exp_tile_hold<BC, MASKED>(tS, col0, row_abs, sl2, m * sl2, mx, pk);
+        if (!__any_sync(0xFFFFFFFFu, (mx - m) * sl2 > kFaRescaleThreshold)) {
+#pragma unroll
+            for (int h = 0; h < BC / 64; ++h) {
+                uint32_t part[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) part[i] = pk[h * 32 + i];
+                tmem_st_32x32b_x32(p_base + h * 32, part);
+            }
+            tmem_st_wait();
+            l += lsum;
+            return true;
+        }
+    } else {
+        // fast path, P to shared memory: exponentials with the running max, tile max on the side
+        lsum = fa_exp_tile<BC, MASKED, true, PTMEM>(tS, p_base, r, col0, row_abs, sl2, m * sl2, mx);
+        have_p = true;
+    }
+    if (__any_sync(0xFFFFFFFFu, (mx - m) * sl2 > kFaRescaleThreshold)) {
+        // raise the max, rescale l and O; exponentials computed with the old max are redone
+        const float m_new = fmaxf(m, mx);
+        const float alpha = ex2_approx((m - m_new) * sl2);
+        l *= alpha;
+        m = m_new;
+        have_p = false;
+        if (!first_tile) {
+            if (!wait_o_ready()) return false;
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tO + c * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                tmem_st_32x32b_x32(tO + c * 32, v);
+            }
+            tmem_st_wait();
+        }
+    }
+    if (!have_p) {
+        float unused;
+        lsum = fa_exp_tile<BC, MASKED, false, PTMEM>(tS, p_base, r, col0, row_abs, sl2, m * sl2, unused);
+    }
+    l += lsum;
+    return true;
+}
+
+}  // namespace deca

@@ -26,8 +26,9 @@ TMEM_COLUMNS = 512
 class FAConfig:
     Br: int = 128  # Q rows per tile (tensor-memory lanes)
     Bc: int = 128  # KV rows per pipeline step
-    stages: int = 2  # K/V shared-memory ring depth
+    stages: int = 2  # K/V shared-memory ring depth (q_tiles = 2: slots of the ring K and V share)
     q_tiles: int = 1  # Q tiles a CTA works on alternately (1 or 2)
+    p_tmem: bool = False  # q_tiles = 2: keep P in tensor memory instead of shared memory
 
     @property
     def threads(self) -> int:
@@ -38,18 +39,24 @@ class FAConfig:
         return asdict(self)
 
     def __str__(self):
-        return f"Br={self.Br},Bc={self.Bc},stages={self.stages},q_tiles={self.q_tiles}"
+        return (f"Br={self.Br},Bc={self.Bc},stages={self.stages},q_tiles={self.q_tiles}"
+                + (",p_tmem=1" if self.p_tmem else ""))
 
 
 def smem_bytes(cfg: FAConfig, D: int) -> int:
     q = cfg.q_tiles * cfg.Br * D * 2
-    kv = 2 * cfg.stages * cfg.Bc * D * 2
-    p = cfg.q_tiles * cfg.Br * cfg.Bc * 2  # P staged in shared memory for the PV product
+    if cfg.q_tiles == 2:
+        kv = cfg.stages * cfg.Bc * D * 2  # one ring shared by K and V tiles
+        p = 0 if cfg.p_tmem else 2 * cfg.Br * cfg.Bc * 2  # one P tile per Q tile
+    else:
+        kv = 2 * cfg.stages * cfg.Bc * D * 2  # a K ring and a V ring
+        p = 2 * cfg.Br * cfg.Bc * 2  # double-buffered P
     return q + kv + p + 2048
 
 
 def tmem_columns(cfg: FAConfig, D: int) -> int:
-    cols = cfg.q_tiles * (cfg.Bc + D)  # S (fp32) and O (fp32) per Q tile
+    # q_tiles = 1: two score buffers + O; q_tiles = 2: one score buffer and one O per Q tile
+    cols = 2 * cfg.Bc + cfg.q_tiles * D
     p = 32
     while p < cols:
         p *= 2
@@ -61,9 +68,11 @@ def check_config(cfg: FAConfig, S_q: int, S_kv: int, D: int) -> None:
     assert cfg.Br == 128
     assert cfg.Bc in (64, 128)
     assert cfg.q_tiles in (1, 2)
-    assert 1 <= cfg.stages <= 4
-    assert S_q % cfg.Br == 0 and S_kv % cfg.Bc == 0
-    assert (S_q // cfg.Br) % cfg.q_tiles == 0
+    if cfg.q_tiles == 2:
+        assert cfg.Bc == 128 and 2 <= cfg.stages <= 8
+    else:
+        assert 1 <= cfg.stages <= 4 and not cfg.p_tmem
+    assert S_q % (cfg.Br * cfg.q_tiles) == 0 and S_kv % cfg.Bc == 0
     assert smem_bytes(cfg, D) <= MAX_DYN_SMEM
     assert tmem_columns(cfg, D) <= TMEM_COLUMNS
 
@@ -91,7 +100,7 @@ def build_flash_attn_to_file(shape, cfg: FAConfig, softmax_scale, arch: str, pat
 def native_cfg(cfg: FAConfig):
     from .. import native
 
-    return native.FaCfg(cfg.Br, cfg.Bc, cfg.stages, cfg.q_tiles)
+    return native.FaCfg(cfg.Br, cfg.Bc, cfg.stages, cfg.q_tiles, int(cfg.p_tmem))
 
 
 def bind(spec: KernelSpec):

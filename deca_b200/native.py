@@ -44,7 +44,7 @@ class GemmCfg(ctypes.Structure):
 
 
 class FaCfg(ctypes.Structure):
-    _fields_ = [(n, ctypes.c_int) for n in ("Br", "Bc", "stages", "q_tiles")]
+    _fields_ = [(n, ctypes.c_int) for n in ("Br", "Bc", "stages", "q_tiles", "p_tmem")]
 
 
 def lib() -> ctypes.CDLL:

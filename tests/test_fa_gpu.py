@@ -42,7 +42,7 @@ def run_native(native, q_bits, k_bits, v_bits, causal, scale=None, cfg=None):
         scale = 1.0 / float(np.sqrt(D))
     ccfg = None
     if cfg is not None:
-        ccfg = ctypes.byref(native.FaCfg(128, cfg.get("Bc", 128), cfg.get("stages", 2), 1))
+        ccfg = ctypes.byref(native.FaCfg(128, cfg.get("Bc", 128), cfg.get("stages", 2), cfg.get("q_tiles", 1), cfg.get("p_tmem", 0)))
     st = native.lib().deca_fa_fwd_f16(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), B, H, S_q, S_kv, D,
                                       ctypes.c_float(scale), int(causal), ccfg,
                                       ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
@@ -78,14 +78,18 @@ def test_cross_attention_lengths(native):
     check(q, k, v, run_native(native, q, k, v, False, scale=0.3), False, scale=0.3)
 
 
-@pytest.mark.parametrize("cfg", [dict(Bc=64, stages=1), dict(Bc=64, stages=3), dict(Bc=128, stages=1), dict(Bc=64, stages=4)],
+@pytest.mark.parametrize("cfg", [dict(Bc=64, stages=1), dict(Bc=64, stages=3), dict(Bc=128, stages=1), dict(Bc=64, stages=4),
+                                 dict(Bc=128, stages=3, q_tiles=2), dict(Bc=128, stages=2, q_tiles=2),
+                                 dict(Bc=128, stages=6, q_tiles=2), dict(Bc=128, stages=4, q_tiles=2, p_tmem=1),
+                                 dict(Bc=128, stages=2, q_tiles=2, p_tmem=1), dict(Bc=128, stages=5, q_tiles=2, p_tmem=1)],
                          ids=lambda c: ",".join(f"{k}={v}" for k, v in c.items()))
 def test_configs_match_oracle(native, cfg):
     for D in (64, 128):
-        if native.lib().deca_fa_fwd_f16_check_config(1, 2, 640, 640, D, 1, ctypes.byref(
-                native.FaCfg(128, cfg["Bc"], cfg["stages"], 1))) != 0:
+        S = 768 if cfg.get("q_tiles", 1) == 2 else 640
+        if native.lib().deca_fa_fwd_f16_check_config(1, 2, S, S, D, 1, ctypes.byref(
+                native.FaCfg(128, cfg["Bc"], cfg["stages"], cfg.get("q_tiles", 1), cfg.get("p_tmem", 0)))) != 0:
             continue
-        q, k, v = make_qkv(1, 2, 640, 640, D, seed=5)
+        q, k, v = make_qkv(1, 2, S, S, D, seed=5)
         for causal in (False, True):
             check(q, k, v, run_native(native, q, k, v, causal, cfg=cfg), causal)
 
@@ -150,6 +154,6 @@ def test_argument_errors(native):
     assert L.deca_fa_fwd_f16(p, p, p, p, 1, 1, 128, 128, 96, f, 0, None, st) == -5
     assert L.deca_fa_fwd_f16(p, p, p, p, 1, 1, 128, 256, 64, f, 1, None, st) == -2  # causal needs S_q == S_kv
     assert L.deca_fa_fwd_f16(p, p, p, p, 1, 1, 100, 128, 64, f, 0, None, st) == -4  # S_q % 128
-    bad = native.FaCfg(128, 128, 4, 1)  # 4 stages of 64 KB do not fit at D = 128
+    bad = native.FaCfg(128, 128, 4, 1, 0)  # 4 stages of 64 KB do not fit at D = 128
     assert L.deca_fa_fwd_f16(p, p, p, p, 1, 1, 128, 128, 128, f, 0, ctypes.byref(bad), st) == -4
     torch.cuda.synchronize()
