@@ -84,12 +84,12 @@ def solve_flash_attn(arch, B: int, H: int, S_q: int, S_kv: int, D: int, type_siz
     bc, st, qt, pt = BitVecs("bc st qt pt", 32)
     s.add(Or(bc == 64, bc == 128))
     s.add(Or(qt == 1, qt == 2))
-    s.add(ULE(pt, 1), Implies(qt == 1, pt == 0))
+    s.add(ULE(pt, 1))
     s.add(URem(BitVecVal(S_kv, 32), bc) == 0)
     s.add(URem(BitVecVal(S_q, 32), 128 * qt) == 0)
     n_kv = UDiv(BitVecVal(S_kv, 32), bc)
     # one Q tile per CTA: a K ring and a V ring of `st` slots, double-buffered P, two score buffers
-    smem1 = (128 * D + 2 * st * bc * D + 2 * 128 * bc) * type_size + 2048
+    smem1 = (128 * D + 2 * st * bc * D + If(pt == 1, BitVecVal(0, 32), BitVecVal(2 * 128, 32) * bc)) * type_size + 2048
     s.add(Implies(qt == 1, And(UGE(st, 1), ULE(st, 4), ULE(st, n_kv), ULE(smem1, arch.max_dyn_smem_per_block),
                                ULE(2 * bc + D, getattr(arch, "tmem_columns", 512)))))
     # two Q tiles per CTA: one ring of `st` slots shared by K and V tiles, one P and one score buffer per tile

@@ -134,8 +134,11 @@ def fa_score(cfg, arch: Arch, shape, causal: bool = False) -> float:
     # two Q tiles per CTA with P in tensor memory: no P traffic through shared memory and the
     # MMAs of one tile overlap the softmax of the other (measured +14 % at D = 128, none at D = 64;
     # with P in shared memory the two-tile schedule measured no faster than one tile)
-    if getattr(cfg, "p_tmem", False) and D >= 128:
-        eff *= 1.14
+    if getattr(cfg, "p_tmem", False):
+        if cfg.q_tiles == 2:
+            eff *= 1.14 if D >= 128 else 1.0
+        else:
+            eff *= 0.97  # one tile: the softmax warps are the critical path either way (measured)
 
     n_q = S_q // cfg.Br
     grid = n_q * B * H

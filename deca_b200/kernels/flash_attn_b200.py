@@ -28,7 +28,7 @@ class FAConfig:
     Bc: int = 128  # KV rows per pipeline step
     stages: int = 2  # K/V shared-memory ring depth (q_tiles = 2: slots of the ring K and V share)
     q_tiles: int = 1  # Q tiles a CTA works on alternately (1 or 2)
-    p_tmem: bool = False  # q_tiles = 2: keep P in tensor memory instead of shared memory
+    p_tmem: bool = False  # keep P in tensor memory (MMA A operand) instead of shared memory
 
     @property
     def threads(self) -> int:
@@ -50,7 +50,7 @@ def smem_bytes(cfg: FAConfig, D: int) -> int:
         p = 0 if cfg.p_tmem else 2 * cfg.Br * cfg.Bc * 2  # one P tile per Q tile
     else:
         kv = 2 * cfg.stages * cfg.Bc * D * 2  # a K ring and a V ring
-        p = 2 * cfg.Br * cfg.Bc * 2  # double-buffered P
+        p = 0 if cfg.p_tmem else 2 * cfg.Br * cfg.Bc * 2  # double-buffered P
     return q + kv + p + 2048
 
 
@@ -71,7 +71,7 @@ def check_config(cfg: FAConfig, S_q: int, S_kv: int, D: int) -> None:
     if cfg.q_tiles == 2:
         assert cfg.Bc == 128 and 2 <= cfg.stages <= 8
     else:
-        assert 1 <= cfg.stages <= 4 and not cfg.p_tmem
+        assert 1 <= cfg.stages <= 4
     assert S_q % (cfg.Br * cfg.q_tiles) == 0 and S_kv % cfg.Bc == 0
     assert smem_bytes(cfg, D) <= MAX_DYN_SMEM
     assert tmem_columns(cfg, D) <= TMEM_COLUMNS

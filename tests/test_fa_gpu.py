@@ -81,7 +81,8 @@ def test_cross_attention_lengths(native):
 @pytest.mark.parametrize("cfg", [dict(Bc=64, stages=1), dict(Bc=64, stages=3), dict(Bc=128, stages=1), dict(Bc=64, stages=4),
                                  dict(Bc=128, stages=3, q_tiles=2), dict(Bc=128, stages=2, q_tiles=2),
                                  dict(Bc=128, stages=6, q_tiles=2), dict(Bc=128, stages=4, q_tiles=2, p_tmem=1),
-                                 dict(Bc=128, stages=2, q_tiles=2, p_tmem=1), dict(Bc=128, stages=5, q_tiles=2, p_tmem=1)],
+                                 dict(Bc=128, stages=2, q_tiles=2, p_tmem=1), dict(Bc=128, stages=5, q_tiles=2, p_tmem=1),
+                                 dict(Bc=128, stages=3, p_tmem=1), dict(Bc=64, stages=2, p_tmem=1), dict(Bc=128, stages=1, p_tmem=1)],
                          ids=lambda c: ",".join(f"{k}={v}" for k, v in c.items()))
 def test_configs_match_oracle(native, cfg):
     for D in (64, 128):
