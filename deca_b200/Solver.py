@@ -94,9 +94,9 @@ def solve_flash_attn(arch, B: int, H: int, S_q: int, S_kv: int, D: int, type_siz
                                ULE(2 * bc + D, getattr(arch, "tmem_columns", 512)))))
     # two Q tiles per CTA: one ring of `st` slots shared by K and V tiles, one P and one score buffer per tile
     smem2 = (2 * 128 * D + st * bc * D + If(pt == 1, BitVecVal(0, 32), BitVecVal(2 * 128, 32) * bc)) * type_size + 2048
-    s.add(Implies(qt == 2, And(bc == 128, UGE(st, 2), ULE(st, 8), ULE(st, 2 * n_kv),
-                               ULE(smem2, arch.max_dyn_smem_per_block),
-                               ULE(2 * bc + 2 * D, getattr(arch, "tmem_columns", 512)))))
+    s.add(Implies(qt == 2, And(Or(bc == 128, pt == 1), UGE(st, If(bc == 64, BitVecVal(4, 32), BitVecVal(2, 32))),
+                               ULE(st, 8), ULE(st, 2 * n_kv), ULE(smem2, arch.max_dyn_smem_per_block),
+                               BitVecVal(int(256 + 2 * D <= getattr(arch, "tmem_columns", 512)), 32) == 1)))
 
     results = []
     for vals in _all_models(s, (bc, st, qt, pt), count):

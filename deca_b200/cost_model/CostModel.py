@@ -135,7 +135,9 @@ def fa_score(cfg, arch: Arch, shape, causal: bool = False) -> float:
     # MMAs of one tile overlap the softmax of the other (measured +14 % at D = 128, none at D = 64;
     # with P in shared memory the two-tile schedule measured no faster than one tile)
     if getattr(cfg, "p_tmem", False):
-        if cfg.q_tiles == 2:
+        if cfg.q_tiles == 2 and cfg.Bc == 64:
+            eff *= 0.6  # two score buffers per tile, but twice the barrier round trips (measured)
+        elif cfg.q_tiles == 2:
             eff *= 1.14 if D >= 128 else 1.0
         else:
             eff *= 0.97  # one tile: the softmax warps are the critical path either way (measured)

@@ -5,7 +5,7 @@
 
 namespace deca {
 
-__device__ DeviceStatus g_device_status = {0u, 0u, 0u, 0u};
+__device__ DeviceStatus g_device_status = {};
 
 DeviceStatus *device_status_ptr() {
     // The symbol has one address per device; cache them.
@@ -37,6 +37,17 @@ extern "C" int deca_last_device_status(int *code, int *where, int *block, int cl
         e = cudaMemset(p, 0, sizeof(h));
         if (e != cudaSuccess) return (int)e;
     }
+    return DECA_OK;
+}
+
+extern "C" int deca_device_status_words(unsigned int *out, int n) {
+    deca::DeviceStatus *p = deca::device_status_ptr();
+    if (!p || !out) return p ? DECA_ERR_NULL : (int)cudaErrorUnknown;
+    deca::DeviceStatus h;
+    cudaError_t e = cudaMemcpy(&h, p, sizeof(h), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return (int)e;
+    const unsigned int *w = reinterpret_cast<const unsigned int *>(&h);
+    for (int i = 0; i < n && i < (int)(sizeof(h) / 4); ++i) out[i] = w[i];
     return DECA_OK;
 }
 

@@ -24,6 +24,9 @@ struct DeviceStatus {
     unsigned int where;  // kernel-specific site id
     unsigned int block;  // linear block id that reported first
     unsigned int pad;
+    // Diagnostics: every role of block (0, 0) that leaves a bounded wait unsuccessfully stores
+    // (site << 16 | loop index) in its own slot, whether or not it was the first to time out.
+    unsigned int detail[12];
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {

@@ -1,4 +1,4 @@
-// FlashAttention forward for B200, two Q tiles per CTA (FAConfig q_tiles = 2, Bc = 128).
+// FlashAttention forward for B200, two Q tiles per CTA (FAConfig q_tiles = 2).
 //
 // Same arithmetic as fa_fwd_f16.cu; what changes is the schedule.  A CTA owns two consecutive
 // 128-row Q tiles of one head (group A = even tile, group B = odd tile) and 320 threads:
@@ -10,8 +10,11 @@
 //               other group is in its softmax.
 //   warps 2-5   softmax + epilogue of group A, warps 6-9 of group B: one thread per query row, two
 //               softmax warps per scheduler.
-// Causal: the pair (2t, 2t+1) visits KV tiles 0..2t+1; group A stops one tile earlier; each
-// group masks its own diagonal tile; pairs are scheduled longest first.
+// With 64-key tiles (BC = 64, P in tensor memory) every group owns TWO score buffers, so the
+// scores of step j+1 are computed while the softmax of step j runs and a group never waits for
+// the tensor pipe; with 128-key tiles tensor memory only has room for one buffer per group.
+// Causal: each group visits the KV tiles up to its own diagonal and masks the tiles that cross it;
+// group A stops 128 keys earlier; pairs are scheduled longest first.
 // All mbarrier waits are bounded (ptx.cuh); a wait that runs out raises the CTA's abort flag and
 // every role falls through to the common teardown.
 #include <atomic>
@@ -25,7 +28,6 @@ namespace deca {
 namespace {
 
 constexpr int kBr = 128;
-constexpr int kBc = 128;
 constexpr int kThreads2 = 320;
 
 struct Fa2Args {
@@ -40,11 +42,14 @@ struct Fa2Args {
 // A operand of the P V product, so neither the P write nor the P read touches shared memory and
 // the K/V ring gets the space; the product of step j must then be issued BEFORE the next score
 // MMA of the same group overwrites that tile.
-template <int D, bool PTMEM>
+template <int D, int BC, bool PTMEM>
 __global__ void __launch_bounds__(kThreads2, 1)
 fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const Fa2Args g) {
     using P16 = Pack16<DECA_F16>;
+    constexpr int kBc = BC;
+    constexpr int NSB = (BC == 64) ? 2 : 1;  // score buffers per group
+    static_assert(BC == 128 || PTMEM, "64-key tiles keep P in tensor memory");
     constexpr uint32_t kQBytes = kBr * D * 2;
     constexpr uint32_t kKVBytes = kBc * D * 2;
     constexpr uint32_t kPBytes = kBr * kBc * 2;
@@ -67,11 +72,16 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     auto kv_full = [&](int i) { return sBar + 8u * (1 + i); };
     auto kv_empty = [&](int i) { return sBar + 8u * (1 + stages + i); };
     const uint32_t fixed0 = sBar + 8u * (1 + 2 * stages);
-    auto s_full = [&](int grp) { return fixed0 + 8u * grp; };
-    auto p_full = [&](int grp) { return fixed0 + 8u * (2 + grp); };
-    auto pv_done = [&](int grp) { return fixed0 + 8u * (4 + grp); };
-    const uint32_t drain_bar = fixed0 + 8u * 6;
-    const uint32_t slot_addr = fixed0 + 8u * 7;
+    auto s_full = [&](int grp, int buf) { return fixed0 + 8u * (grp * 2 + buf); };
+    // one "P ready" barrier per score buffer: with two buffers a group may finish two tiles before
+    // the MMA warp looks, and a single barrier would then have gone through two phases
+    auto p_full = [&](int grp, int buf) { return fixed0 + 8u * (4 + grp * 2 + buf); };
+    // likewise one "product done" barrier per score buffer: tile j uses buffer j % NSB, and the
+    // product of tile j - NSB is always complete before the softmax of tile j starts, so a wait on
+    // the buffer's barrier can only be one phase behind
+    auto pv_done = [&](int grp, int buf) { return fixed0 + 8u * (8 + grp * 2 + buf); };
+    const uint32_t drain_bar = fixed0 + 8u * 12;
+    const uint32_t slot_addr = fixed0 + 8u * 13;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + (slot_addr - base));
     volatile uint32_t *abort_flag = tmem_slot + 1;
 
@@ -84,8 +94,8 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const int q_row0 = bh * g.S_q + pair * 2 * kBr;  // first row of tile A in the [B*H*S_q, D] view
     const int kv_row0 = bh * g.S_kv;
     // KV tiles visited by group A / B (B always visits at least as many as A)
-    const int n_a = g.causal ? 2 * pair + 1 : g.S_kv / kBc;
-    const int n_b = g.causal ? 2 * pair + 2 : g.S_kv / kBc;
+    const int n_a = g.causal ? ((2 * pair + 1) * kBr + kBc - 1) / kBc : g.S_kv / kBc;
+    const int n_b = g.causal ? ((2 * pair + 2) * kBr + kBc - 1) / kBc : g.S_kv / kBc;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -95,9 +105,12 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             mbar_init(kv_empty(i), 1);
         }
         for (int grp = 0; grp < 2; ++grp) {
-            mbar_init(s_full(grp), 1);
-            mbar_init(p_full(grp), 4);
-            mbar_init(pv_done(grp), 1);
+            mbar_init(s_full(grp, 0), 1);
+            mbar_init(s_full(grp, 1), 1);
+            mbar_init(p_full(grp, 0), 4);
+            mbar_init(p_full(grp, 1), 4);
+            mbar_init(pv_done(grp, 0), 1);
+            mbar_init(pv_done(grp, 1), 1);
         }
         mbar_init(drain_bar, 1);
         fence_barrier_init();
@@ -114,8 +127,8 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    auto tS = [&](int grp) { return tmem_base + (uint32_t)(grp * kBc); };
-    auto tO = [&](int grp) { return tmem_base + 2u * kBc + (uint32_t)(grp * D); };
+    auto tS = [&](int grp, int buf) { return tmem_base + (uint32_t)((grp * NSB + buf) * kBc); };
+    auto tO = [&](int grp) { return tmem_base + 2u * NSB * kBc + (uint32_t)(grp * D); };
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -132,6 +145,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             int n_items = 0;
             for (int i = 0; i < 2 * n_b; ++i) {  // item 2j = K_j, 2j + 1 = V_j
                 if (!mbar_wait(kv_empty(s), ph ^ 1u, abort_flag)) {
+                    report_detail(g.status, 0, 1, i);
                     ok = false;
                     break;
                 }
@@ -166,16 +180,16 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             // ring slot / parity of item i
             auto slot_of = [&](int i) { return i % stages; };
             auto par_of = [&](int i) { return (uint32_t)((i / stages) & 1); };
-            auto issue_qk = [&](int grp, int j) {  // S_grp = Q_grp K_j^T
+            auto issue_qk = [&](int grp, int j) {  // S_grp[j % NSB] = Q_grp K_j^T
                 const uint32_t kb = sKV + slot_of(2 * j) * kKVBytes;
                 const uint32_t qb = sQ + grp * kQBytes;
 #pragma unroll
                 for (int kd = 0; kd < D / 16; ++kd) {
                     const uint64_t adesc = make_smem_desc(qb + (kd / 4) * 16384 + (kd % 4) * 32, 16, 1024);
                     const uint64_t bdesc = make_smem_desc(kb + (kd / 4) * kKVBlock + (kd % 4) * 32, 16, 1024);
-                    umma_f16_ss(tS(grp), adesc, bdesc, kIdescQK, kd != 0 ? 1u : 0u);
+                    umma_f16_ss(tS(grp, j % NSB), adesc, bdesc, kIdescQK, kd != 0 ? 1u : 0u);
                 }
-                umma_commit(s_full(grp));
+                umma_commit(s_full(grp, j % NSB));
             };
             auto issue_pv = [&](int grp, int j) {  // O_grp (+)= P_grp V_j
                 const uint32_t pb = sP + grp * kPBytes;
@@ -185,43 +199,60 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     const uint64_t bdesc = make_smem_desc(vb + kk * 2048, kKVBlock, 1024);
                     if constexpr (PTMEM) {
                         // 16 keys = 8 packed columns of the P tile in tensor memory
-                        umma_f16_ts(tO(grp), tS(grp) + kk * 8, bdesc, kIdescPV, (j | kk) != 0 ? 1u : 0u);
+                        umma_f16_ts(tO(grp), tS(grp, j % NSB) + kk * 8, bdesc, kIdescPV, (j | kk) != 0 ? 1u : 0u);
                     } else {
                         const uint64_t adesc = make_smem_desc(pb + (kk / 4) * 16384 + (kk % 4) * 32, 16, 1024);
                         umma_f16_ss(tO(grp), adesc, bdesc, kIdescPV, (j | kk) != 0 ? 1u : 0u);
                     }
                 }
-                umma_commit(pv_done(grp));
+                umma_commit(pv_done(grp, j % NSB));
             };
-            ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(kv_full(slot_of(0)), par_of(0), abort_flag);
-            if (ok) {
+            // prologue: fill every score buffer (tiles 0 .. NSB-1 of both groups)
+            ok = mbar_wait(q_full, 0, abort_flag);
+            for (int t = 0; t < NSB && t < n_b && ok; ++t) {
+                if (!mbar_wait(kv_full(slot_of(2 * t)), par_of(2 * t), abort_flag)) {
+                    report_detail(g.status, 1, 2, t);
+                    ok = false;
+                    break;
+                }
                 tc_fence_after_sync();
-                issue_qk(0, 0);
-                issue_qk(1, 0);
-                umma_commit(kv_empty(slot_of(0)));
+                if (t < n_a) issue_qk(0, t);
+                issue_qk(1, t);
+                umma_commit(kv_empty(slot_of(2 * t)));
             }
             for (int j = 0; j < n_b && ok; ++j) {
-                // K_{j+1} (if any) and V_j must have landed
-                if (j + 1 < n_b && !mbar_wait(kv_full(slot_of(2 * j + 2)), par_of(2 * j + 2), abort_flag)) ok = false;
-                if (ok && !mbar_wait(kv_full(slot_of(2 * j + 1)), par_of(2 * j + 1), abort_flag)) ok = false;
+                const int jn = j + NSB;  // tile whose scores are issued in this step
+                const uint32_t p_par = (uint32_t)((j / NSB) & 1);
+                // V_j and K_jn (if any) must have landed
+                if (!mbar_wait(kv_full(slot_of(2 * j + 1)), par_of(2 * j + 1), abort_flag)) {
+                    report_detail(g.status, 1, 4, j);
+                    ok = false;
+                }
+                if (ok && jn < n_b && !mbar_wait(kv_full(slot_of(2 * jn)), par_of(2 * jn), abort_flag)) {
+                    report_detail(g.status, 1, 3, j);
+                    ok = false;
+                }
                 if (!ok) break;
-                // group A: once P_A(j) is ready S_A is free as well
+                // group A: once P_A(j) is ready its score buffer is consumed as well
                 if (j < n_a) {
-                    if (!mbar_wait(p_full(0), (uint32_t)(j & 1), abort_flag)) {
+                    if (!mbar_wait(p_full(0, j % NSB), p_par, abort_flag)) {
+                        report_detail(g.status, 1, 5, j);
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
                     if constexpr (PTMEM) {
+                        // the product reads P from the buffer the next score MMA overwrites
                         issue_pv(0, j);
-                        if (j + 1 < n_a) issue_qk(0, j + 1);
+                        if (jn < n_a) issue_qk(0, jn);
                     } else {
-                        if (j + 1 < n_a) issue_qk(0, j + 1);
+                        if (jn < n_a) issue_qk(0, jn);
                         issue_pv(0, j);
                     }
                 }
-                // group B (always the last user of K_{j+1} and V_j)
-                if (!mbar_wait(p_full(1), (uint32_t)(j & 1), abort_flag)) {
+                // group B (always the last user of K_jn and V_j)
+                if (!mbar_wait(p_full(1, j % NSB), p_par, abort_flag)) {
+                    report_detail(g.status, 1, 6, j);
                     ok = false;
                     break;
                 }
@@ -229,14 +260,14 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 if constexpr (PTMEM) {
                     issue_pv(1, j);
                     umma_commit(kv_empty(slot_of(2 * j + 1)));
-                    if (j + 1 < n_b) {
-                        issue_qk(1, j + 1);
-                        umma_commit(kv_empty(slot_of(2 * j + 2)));
+                    if (jn < n_b) {
+                        issue_qk(1, jn);
+                        umma_commit(kv_empty(slot_of(2 * jn)));
                     }
                 } else {
-                    if (j + 1 < n_b) {
-                        issue_qk(1, j + 1);
-                        umma_commit(kv_empty(slot_of(2 * j + 2)));
+                    if (jn < n_b) {
+                        issue_qk(1, jn);
+                        umma_commit(kv_empty(slot_of(2 * jn)));
                     }
                     issue_pv(1, j);
                     umma_commit(kv_empty(slot_of(2 * j + 1)));
@@ -263,9 +294,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int qt = 2 * pair + grp;
         const int row_abs = qt * kBr + r;
         const int n_kv = grp == 0 ? n_a : n_b;
-        const uint32_t tSg = tS(grp) + lane_off;
         const uint32_t tOg = tO(grp) + lane_off;
-        const uint32_t pb = PTMEM ? tSg : sP + grp * kPBytes;
         const float sl2 = g.sl2;
         float m = kNegInf, l = 0.f;
         bool ok = true;
@@ -274,22 +303,31 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         };
 
         for (int j = 0; j < n_kv; ++j) {
-            if (!wait_all(s_full(grp), (uint32_t)(j & 1))) {
+            const int buf = j % NSB;
+            if (!wait_all(s_full(grp, buf), (uint32_t)((j / NSB) & 1))) {
+                if (lane == 0 && q == 0) report_detail(g.status, 2 + grp, 7, j);
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
+            const uint32_t tSg = tS(grp, buf) + lane_off;
+            const uint32_t pb = PTMEM ? tSg : sP + grp * kPBytes;
             const bool diag = g.causal && ((j + 1) * kBc - 1 > qt * kBr);
             const int col0 = j * kBc;
 
             // P (single buffer per group) was last read by the product of tile j - 1, which is also
             // the product that completes O for a rescale
-            auto wait_prev = [&]() { return j == 0 || wait_all(pv_done(grp), (uint32_t)((j - 1) & 1)); };
+            auto wait_prev = [&]() {
+                return j == 0 || wait_all(pv_done(grp, (j - 1) % NSB), (uint32_t)(((j - 1) / NSB) & 1));
+            };
+            // P in tensor memory reuses the score buffer that was just filled: free by construction
+            auto wait_p = [&]() { return PTMEM || wait_prev(); };
             const bool step_ok = diag ? fa_softmax_step<kBc, D, true, PTMEM>(tSg, tOg, pb, r, col0, row_abs, sl2, j == 0,
-                                                                             m, l, wait_prev, wait_prev)
+                                                                             m, l, wait_p, wait_prev)
                                       : fa_softmax_step<kBc, D, false, PTMEM>(tSg, tOg, pb, r, col0, row_abs, sl2, j == 0,
-                                                                              m, l, wait_prev, wait_prev);
+                                                                              m, l, wait_p, wait_prev);
             if (!step_ok) {
+                if (lane == 0 && q == 0) report_detail(g.status, 2 + grp, 8, j);
                 ok = false;
                 break;
             }
@@ -297,10 +335,13 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             fence_proxy_async_smem();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full(grp));
+            if (lane == 0) mbar_arrive(p_full(grp, buf));
         }
 
-        if (ok) ok = wait_all(pv_done(grp), (uint32_t)((n_kv - 1) & 1));
+        if (ok) {
+            ok = wait_all(pv_done(grp, (n_kv - 1) % NSB), (uint32_t)(((n_kv - 1) / NSB) & 1));
+            if (!ok && lane == 0 && q == 0) report_detail(g.status, 2 + grp, 9, n_kv);
+        }
         if (!ok) {
             if (lane == 0 && *abort_flag == 0) {
                 *abort_flag = 1;
@@ -353,32 +394,34 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
 }
 
-template <int D, bool PTMEM>
+template <int D, int BC, bool PTMEM>
 int launch_fa2(const CUtensorMap &tmQ, const CUtensorMap &tmK, const CUtensorMap &tmV, const CUtensorMap &tmO,
                const Fa2Args &g, dim3 grid, size_t smem, cudaStream_t st) {
     static std::atomic<size_t> configured{0};
     if (configured.load(std::memory_order_relaxed) < smem) {
-        cudaError_t e = cudaFuncSetAttribute(fa_fwd2_kernel<D, PTMEM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(fa_fwd2_kernel<D, BC, PTMEM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured.store(smem, std::memory_order_relaxed);
     }
-    fa_fwd2_kernel<D, PTMEM><<<grid, kThreads2, smem, st>>>(tmQ, tmK, tmV, tmO, g);
+    fa_fwd2_kernel<D, BC, PTMEM><<<grid, kThreads2, smem, st>>>(tmQ, tmK, tmV, tmO, g);
     return (int)cudaGetLastError();
 }
 
 }  // namespace
 
-size_t fa2_smem_bytes(int D, int stages, bool ptmem) {
-    return 1024 + 2 * (size_t)kBr * D * 2 + (ptmem ? 0 : 2 * (size_t)kBr * kBc * 2) + (size_t)stages * kBc * D * 2 +
-           8 * (2 * (size_t)stages + 16);
+size_t fa2_smem_bytes(int D, int BC, int stages, bool ptmem) {
+    return 1024 + 2 * (size_t)kBr * D * 2 + (ptmem ? 0 : 2 * (size_t)kBr * BC * 2) + (size_t)stages * BC * D * 2 +
+           8 * (2 * (size_t)stages + 20);
 }
 
 // Host rules of the two-tile schedule; shared with deca_fa_fwd_f16_check_config.
 int fa2_check(int S_q, int S_kv, int D, const deca_fa_cfg &c) {
-    if (c.Bc != kBc || c.Br != kBr) return DECA_ERR_CONFIG;
-    if (S_q % (2 * kBr) != 0 || S_kv % kBc != 0) return DECA_ERR_CONFIG;
-    if (c.stages < 2 || c.stages > 8) return DECA_ERR_CONFIG;
-    if (fa2_smem_bytes(D, c.stages, c.p_tmem != 0) > 232448) return DECA_ERR_CONFIG;
+    if (c.Br != kBr || (c.Bc != 128 && c.Bc != 64)) return DECA_ERR_CONFIG;
+    if (c.Bc == 64 && !c.p_tmem) return DECA_ERR_CONFIG;  // 64-key tiles keep P in tensor memory
+    if (S_q % (2 * kBr) != 0 || S_kv % c.Bc != 0) return DECA_ERR_CONFIG;
+    // 64-key tiles keep two score tiles per group in flight: K_{j+2} and V_j live together
+    if (c.stages < (c.Bc == 64 ? 4 : 2) || c.stages > 8) return DECA_ERR_CONFIG;
+    if (fa2_smem_bytes(D, c.Bc, c.stages, c.p_tmem != 0) > 232448) return DECA_ERR_CONFIG;
     return DECA_OK;
 }
 
@@ -394,12 +437,15 @@ int fa2_launch(const CUtensorMap &tmQ, const CUtensorMap &tmK, const CUtensorMap
     if (!g.status) return (int)cudaErrorUnknown;
     const dim3 grid((unsigned)(S_q / (2 * kBr)), (unsigned)(B * H), 1);
     const bool ptmem = c.p_tmem != 0;
-    const size_t smem = fa2_smem_bytes(D, c.stages, ptmem);
+    const size_t smem = fa2_smem_bytes(D, c.Bc, c.stages, ptmem);
+    if (c.Bc == 64)
+        return D == 128 ? launch_fa2<128, 64, true>(tmQ, tmK, tmV, tmO, g, grid, smem, st)
+                        : launch_fa2<64, 64, true>(tmQ, tmK, tmV, tmO, g, grid, smem, st);
     if (ptmem)
-        return D == 128 ? launch_fa2<128, true>(tmQ, tmK, tmV, tmO, g, grid, smem, st)
-                        : launch_fa2<64, true>(tmQ, tmK, tmV, tmO, g, grid, smem, st);
-    return D == 128 ? launch_fa2<128, false>(tmQ, tmK, tmV, tmO, g, grid, smem, st)
-                    : launch_fa2<64, false>(tmQ, tmK, tmV, tmO, g, grid, smem, st);
+        return D == 128 ? launch_fa2<128, 128, true>(tmQ, tmK, tmV, tmO, g, grid, smem, st)
+                        : launch_fa2<64, 128, true>(tmQ, tmK, tmV, tmO, g, grid, smem, st);
+    return D == 128 ? launch_fa2<128, 128, false>(tmQ, tmK, tmV, tmO, g, grid, smem, st)
+                    : launch_fa2<64, 128, false>(tmQ, tmK, tmV, tmO, g, grid, smem, st);
 }
 
 }  // namespace deca

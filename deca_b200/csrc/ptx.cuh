@@ -224,6 +224,11 @@ __device__ __forceinline__ void report_timeout(DeviceStatus *st, unsigned where)
     }
 }
 
+// Diagnostics slot of one role (see DeviceStatus::detail); only block (0, 0) writes.
+__device__ __forceinline__ void report_detail(DeviceStatus *st, int slot, unsigned site, unsigned index) {
+    if (blockIdx.x == 0 && blockIdx.y == 0) st->detail[slot] = (site << 16) | (index & 0xFFFFu);
+}
+
 // Host: device address of the status word on the current device (nullptr on error).
 DeviceStatus *device_status_ptr();
 

@@ -55,8 +55,9 @@ def smem_bytes(cfg: FAConfig, D: int) -> int:
 
 
 def tmem_columns(cfg: FAConfig, D: int) -> int:
-    # q_tiles = 1: two score buffers + O; q_tiles = 2: one score buffer and one O per Q tile
-    cols = 2 * cfg.Bc + cfg.q_tiles * D
+    # q_tiles = 1: two score buffers + O; q_tiles = 2: per Q tile one 128-key or two 64-key score
+    # buffers and one O
+    cols = (2 * cfg.Bc if cfg.q_tiles == 1 else 256) + cfg.q_tiles * D
     p = 32
     while p < cols:
         p *= 2
@@ -69,7 +70,9 @@ def check_config(cfg: FAConfig, S_q: int, S_kv: int, D: int) -> None:
     assert cfg.Bc in (64, 128)
     assert cfg.q_tiles in (1, 2)
     if cfg.q_tiles == 2:
-        assert cfg.Bc == 128 and 2 <= cfg.stages <= 8
+        # 64-key tiles: P must live in tensor memory and K_{j+2}, V_j, V_{j+1} are in flight together
+        assert cfg.Bc == 128 or cfg.p_tmem
+        assert (4 if cfg.Bc == 64 else 2) <= cfg.stages <= 8
     else:
         assert 1 <= cfg.stages <= 4
     assert S_q % (cfg.Br * cfg.q_tiles) == 0 and S_kv % cfg.Bc == 0

@@ -70,6 +70,7 @@ def lib() -> ctypes.CDLL:
         L.deca_fa_fwd_f16.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, ctypes.POINTER(FaCfg), vp]
         ip = ctypes.POINTER(ci)
         L.deca_last_device_status.argtypes = [ip, ip, ip, ci]
+        L.deca_device_status_words.argtypes = [ctypes.POINTER(ctypes.c_uint), ci]
         _lib = L
     return _lib
 
@@ -94,3 +95,10 @@ def last_device_status(clear: bool = True):
     check(lib().deca_last_device_status(ctypes.byref(c), ctypes.byref(w), ctypes.byref(b), int(clear)),
           "deca_last_device_status")
     return c.value, w.value, b.value
+
+
+def device_status_words(n: int = 16):
+    """The raw status record (see deca_device_status_words); for diagnosing a timeout."""
+    buf = (ctypes.c_uint * 16)()
+    check(lib().deca_device_status_words(buf, n), "deca_device_status_words")
+    return [int(x) for x in buf[:n]]

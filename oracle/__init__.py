@@ -55,6 +55,17 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def set_num_threads(n: int | None = None) -> int:
+    """Uses ``n`` OpenMP threads (default: every core the process may run on); returns the count."""
+    if n is None:
+        try:
+            n = len(os.sched_getaffinity(0))
+        except AttributeError:
+            n = os.cpu_count() or 1
+    lib().oracle_set_num_threads(int(n))
+    return num_threads()
+
+
 def _p(a):
     return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
 

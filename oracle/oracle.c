@@ -267,6 +267,17 @@ void oracle_attention_blockwise(const uint16_t *q, const uint16_t *k, const uint
     }
 }
 
+/* Sets the number of OpenMP threads used by the functions above (launchers such as torchrun
+ * export OMP_NUM_THREADS=1, which would otherwise make the CPU arm single-threaded). */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    extern void omp_set_num_threads(int);
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int oracle_num_threads(void) {
     int n = 1;
 #ifdef _OPENMP

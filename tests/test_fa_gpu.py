@@ -82,7 +82,9 @@ def test_cross_attention_lengths(native):
                                  dict(Bc=128, stages=3, q_tiles=2), dict(Bc=128, stages=2, q_tiles=2),
                                  dict(Bc=128, stages=6, q_tiles=2), dict(Bc=128, stages=4, q_tiles=2, p_tmem=1),
                                  dict(Bc=128, stages=2, q_tiles=2, p_tmem=1), dict(Bc=128, stages=5, q_tiles=2, p_tmem=1),
-                                 dict(Bc=128, stages=3, p_tmem=1), dict(Bc=64, stages=2, p_tmem=1), dict(Bc=128, stages=1, p_tmem=1)],
+                                 dict(Bc=128, stages=3, p_tmem=1), dict(Bc=64, stages=2, p_tmem=1), dict(Bc=128, stages=1, p_tmem=1),
+                                 dict(Bc=64, stages=4, q_tiles=2, p_tmem=1), dict(Bc=64, stages=8, q_tiles=2, p_tmem=1),
+                                 dict(Bc=64, stages=5, q_tiles=2, p_tmem=1)],
                          ids=lambda c: ",".join(f"{k}={v}" for k, v in c.items()))
 def test_configs_match_oracle(native, cfg):
     for D in (64, 128):
