@@ -302,14 +302,24 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag)) != 0;
         };
 
+#ifdef DECA_FA_PROFILE
+        long long t_wait = 0, t_step = 0, t_sig = 0, t_all = clock64();
+#endif
         for (int j = 0; j < n_kv; ++j) {
             const int buf = j % NSB;
+#ifdef DECA_FA_PROFILE
+            long long c0 = clock64();
+#endif
             if (!wait_all(s_full(grp, buf), (uint32_t)((j / NSB) & 1))) {
                 if (lane == 0 && q == 0) report_detail(g.status, 2 + grp, 7, j);
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
+#ifdef DECA_FA_PROFILE
+            long long c1 = clock64();
+            t_wait += c1 - c0;
+#endif
             const uint32_t tSg = tS(grp, buf) + lane_off;
             const uint32_t pb = PTMEM ? tSg : sP + grp * kPBytes;
             const bool diag = g.causal && ((j + 1) * kBc - 1 > qt * kBr);
@@ -331,12 +341,27 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 ok = false;
                 break;
             }
+#ifdef DECA_FA_PROFILE
+            long long c2 = clock64();
+            t_step += c2 - c1;
+#endif
             // S is consumed, P (and a possibly rescaled O) are ready
             fence_proxy_async_smem();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full(grp, buf));
+#ifdef DECA_FA_PROFILE
+            t_sig += clock64() - c2;
+#endif
         }
+#ifdef DECA_FA_PROFILE
+        if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && q == 0) {
+            g.status->detail[4 + grp * 4 + 0] = (unsigned)(t_wait / n_kv);
+            g.status->detail[4 + grp * 4 + 1] = (unsigned)(t_step / n_kv);
+            g.status->detail[4 + grp * 4 + 2] = (unsigned)(t_sig / n_kv);
+            g.status->detail[4 + grp * 4 + 3] = (unsigned)((clock64() - t_all) / n_kv);
+        }
+#endif
 
         if (ok) {
             ok = wait_all(pv_done(grp, (n_kv - 1) % NSB), (uint32_t)(((n_kv - 1) / NSB) & 1));

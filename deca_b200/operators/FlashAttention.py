@@ -43,12 +43,13 @@ class FlashAttention(Operator):
         return build_flash_attn(mod)
 
     def default_config(self) -> FAConfig:
-        # measured on B200 at B4 H16 S4096: two Q tiles per CTA with P in tensor memory is the
-        # fastest schedule at D = 128 (0.96 PFLOPS non-causal); D = 64 prefers 64-key tiles
-        if self.S_q % 256 == 0 and self.S_kv % 128 == 0 and (self.D == 128 or self.S_kv % 64 != 0):
-            return FAConfig(Bc=128, stages=4, q_tiles=2, p_tmem=True)
+        # measured on B200 over the FlashAttention-2 grid: at D = 128 two Q tiles per CTA with P in
+        # tensor memory win (0.97 PFLOPS at S = 4096); at D = 64 one Q tile, 64-key tiles, P in
+        # tensor memory (0.53-0.56 PFLOPS)
         if self.D == 64 and self.S_kv % 64 == 0:
-            return FAConfig(Bc=64, stages=3)
+            return FAConfig(Bc=64, stages=2, p_tmem=True)
+        if self.S_q % 256 == 0 and self.S_kv % 128 == 0:
+            return FAConfig(Bc=128, stages=4 if self.S_kv >= 512 else 2, q_tiles=2, p_tmem=True)
         if self.S_kv % 128 == 0:
             return FAConfig(Bc=128, stages=2)
         return FAConfig(Bc=64, stages=2)
