@@ -177,102 +177,156 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             bool ok = true;
-            // ring slot / parity of item i
-            auto slot_of = [&](int i) { return i % stages; };
-            auto par_of = [&](int i) { return (uint32_t)((i / stages) & 1); };
-            auto issue_qk = [&](int grp, int j) {  // S_grp[j % NSB] = Q_grp K_j^T
-                const uint32_t kb = sKV + slot_of(2 * j) * kKVBytes;
-                const uint32_t qb = sQ + grp * kQBytes;
+            // One thread issues every MMA of the CTA, so its instruction stream is on the critical
+            // path: descriptors are a constant upper word plus (address >> 4), the per-step offsets
+            // are compile-time constants, and ring positions advance incrementally (no division).
+            constexpr uint64_t kDescK = (uint64_t(16 >> 4) << 16) | (uint64_t(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+            constexpr uint64_t kDescV = (uint64_t((kKVBlock >> 4) & 0x3FFF) << 16) | (uint64_t(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+            const uint64_t q_desc[2] = {kDescK | (uint64_t)((sQ & 0x3FFFFu) >> 4),
+                                        kDescK | (uint64_t)(((sQ + kQBytes) & 0x3FFFFu) >> 4)};
+            const uint64_t p_desc[2] = {kDescK | (uint64_t)((sP & 0x3FFFFu) >> 4),
+                                        kDescK | (uint64_t)(((sP + kPBytes) & 0x3FFFFu) >> 4)};
+            struct RingPos {
+                int slot;
+                uint32_t par;
+            };
+            auto advance2 = [&](RingPos &p) {  // two items further (K_t -> K_{t+1}, V_j -> V_{j+1})
+                p.slot += 2;
+                if (p.slot >= stages) p.slot -= stages, p.par ^= 1u;
+            };
+            auto issue_qk = [&](int grp, int buf, const RingPos &kp) {  // S_grp[buf] = Q_grp K^T
+                const uint64_t kdesc = kDescK | (uint64_t)(((sKV + kp.slot * kKVBytes) & 0x3FFFFu) >> 4);
+                const uint32_t d_tmem = tS(grp, buf);
 #pragma unroll
                 for (int kd = 0; kd < D / 16; ++kd) {
-                    const uint64_t adesc = make_smem_desc(qb + (kd / 4) * 16384 + (kd % 4) * 32, 16, 1024);
-                    const uint64_t bdesc = make_smem_desc(kb + (kd / 4) * kKVBlock + (kd % 4) * 32, 16, 1024);
-                    umma_f16_ss(tS(grp, j % NSB), adesc, bdesc, kIdescQK, kd != 0 ? 1u : 0u);
+                    umma_f16_ss(d_tmem, q_desc[grp] + (((kd / 4) * 16384 + (kd % 4) * 32) >> 4),
+                                kdesc + (((kd / 4) * kKVBlock + (kd % 4) * 32) >> 4), kIdescQK, kd != 0 ? 1u : 0u);
                 }
-                umma_commit(s_full(grp, j % NSB));
+                umma_commit(s_full(grp, buf));
             };
-            auto issue_pv = [&](int grp, int j) {  // O_grp (+)= P_grp V_j
-                const uint32_t pb = sP + grp * kPBytes;
-                const uint32_t vb = sKV + slot_of(2 * j + 1) * kKVBytes;
+            auto issue_pv = [&](int grp, int buf, const RingPos &vp, uint32_t first) {  // O_grp (+)= P_grp V
+                const uint64_t vdesc = kDescV | (uint64_t)(((sKV + vp.slot * kKVBytes) & 0x3FFFFu) >> 4);
+                const uint32_t d_tmem = tO(grp);
+                const uint32_t a_tmem = tS(grp, buf);
 #pragma unroll
                 for (int kk = 0; kk < kBc / 16; ++kk) {
-                    const uint64_t bdesc = make_smem_desc(vb + kk * 2048, kKVBlock, 1024);
                     if constexpr (PTMEM) {
                         // 16 keys = 8 packed columns of the P tile in tensor memory
-                        umma_f16_ts(tO(grp), tS(grp, j % NSB) + kk * 8, bdesc, kIdescPV, (j | kk) != 0 ? 1u : 0u);
+                        umma_f16_ts(d_tmem, a_tmem + kk * 8, vdesc + kk * (2048 >> 4), kIdescPV, (first | kk) != 0 ? 1u : 0u);
                     } else {
-                        const uint64_t adesc = make_smem_desc(pb + (kk / 4) * 16384 + (kk % 4) * 32, 16, 1024);
-                        umma_f16_ss(tO(grp), adesc, bdesc, kIdescPV, (j | kk) != 0 ? 1u : 0u);
+                        umma_f16_ss(d_tmem, p_desc[grp] + (((kk / 4) * 16384 + (kk % 4) * 32) >> 4),
+                                    vdesc + kk * (2048 >> 4), kIdescPV, (first | kk) != 0 ? 1u : 0u);
                     }
                 }
-                umma_commit(pv_done(grp, j % NSB));
+                umma_commit(pv_done(grp, buf));
             };
+            // ring positions: kp = K tile whose scores are issued next, vp = V_j
+            RingPos kp{0, 0u}, vp{1 % stages, (uint32_t)((1 / stages) & 1)};
             // prologue: fill every score buffer (tiles 0 .. NSB-1 of both groups)
             ok = mbar_wait(q_full, 0, abort_flag);
             for (int t = 0; t < NSB && t < n_b && ok; ++t) {
-                if (!mbar_wait(kv_full(slot_of(2 * t)), par_of(2 * t), abort_flag)) {
+                if (!mbar_wait(kv_full(kp.slot), kp.par, abort_flag)) {
                     report_detail(g.status, 1, 2, t);
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
-                if (t < n_a) issue_qk(0, t);
-                issue_qk(1, t);
-                umma_commit(kv_empty(slot_of(2 * t)));
+                if (t < n_a) issue_qk(0, t % NSB, kp);
+                issue_qk(1, t % NSB, kp);
+                umma_commit(kv_empty(kp.slot));
+                advance2(kp);
             }
+            int buf = 0;
+            uint32_t p_par = 0;
+#ifdef DECA_FA_PROFILE
+            long long m_kv = 0, m_pa = 0, m_pb = 0, m_issue = 0, m_t0 = clock64();
+#endif
             for (int j = 0; j < n_b && ok; ++j) {
-                const int jn = j + NSB;  // tile whose scores are issued in this step
-                const uint32_t p_par = (uint32_t)((j / NSB) & 1);
+#ifdef DECA_FA_PROFILE
+                long long c0 = clock64();
+#endif
+                const int jn = j + NSB;  // tile whose scores are issued in this step (its K is at kp)
                 // V_j and K_jn (if any) must have landed
-                if (!mbar_wait(kv_full(slot_of(2 * j + 1)), par_of(2 * j + 1), abort_flag)) {
+                if (!mbar_wait(kv_full(vp.slot), vp.par, abort_flag)) {
                     report_detail(g.status, 1, 4, j);
                     ok = false;
                 }
-                if (ok && jn < n_b && !mbar_wait(kv_full(slot_of(2 * jn)), par_of(2 * jn), abort_flag)) {
+                if (ok && jn < n_b && !mbar_wait(kv_full(kp.slot), kp.par, abort_flag)) {
                     report_detail(g.status, 1, 3, j);
                     ok = false;
                 }
                 if (!ok) break;
+#ifdef DECA_FA_PROFILE
+                long long c1 = clock64();
+                m_kv += c1 - c0;
+#endif
                 // group A: once P_A(j) is ready its score buffer is consumed as well
                 if (j < n_a) {
-                    if (!mbar_wait(p_full(0, j % NSB), p_par, abort_flag)) {
+                    if (!mbar_wait(p_full(0, buf), p_par, abort_flag)) {
                         report_detail(g.status, 1, 5, j);
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
+#ifdef DECA_FA_PROFILE
+                    long long c2 = clock64();
+                    m_pa += c2 - c1;
+                    c1 = c2;
+#endif
                     if constexpr (PTMEM) {
                         // the product reads P from the buffer the next score MMA overwrites
-                        issue_pv(0, j);
-                        if (jn < n_a) issue_qk(0, jn);
+                        issue_pv(0, buf, vp, (uint32_t)j);
+                        if (jn < n_a) issue_qk(0, buf, kp);
                     } else {
-                        if (jn < n_a) issue_qk(0, jn);
-                        issue_pv(0, j);
+                        if (jn < n_a) issue_qk(0, buf, kp);
+                        issue_pv(0, buf, vp, (uint32_t)j);
                     }
                 }
+#ifdef DECA_FA_PROFILE
+                long long c3 = clock64();
+                m_issue += c3 - c1;
+#endif
                 // group B (always the last user of K_jn and V_j)
-                if (!mbar_wait(p_full(1, j % NSB), p_par, abort_flag)) {
+                if (!mbar_wait(p_full(1, buf), p_par, abort_flag)) {
                     report_detail(g.status, 1, 6, j);
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
+#ifdef DECA_FA_PROFILE
+                long long c4 = clock64();
+                m_pb += c4 - c3;
+#endif
                 if constexpr (PTMEM) {
-                    issue_pv(1, j);
-                    umma_commit(kv_empty(slot_of(2 * j + 1)));
+                    issue_pv(1, buf, vp, (uint32_t)j);
+                    umma_commit(kv_empty(vp.slot));
                     if (jn < n_b) {
-                        issue_qk(1, jn);
-                        umma_commit(kv_empty(slot_of(2 * jn)));
+                        issue_qk(1, buf, kp);
+                        umma_commit(kv_empty(kp.slot));
                     }
                 } else {
                     if (jn < n_b) {
-                        issue_qk(1, jn);
-                        umma_commit(kv_empty(slot_of(2 * jn)));
+                        issue_qk(1, buf, kp);
+                        umma_commit(kv_empty(kp.slot));
                     }
-                    issue_pv(1, j);
-                    umma_commit(kv_empty(slot_of(2 * j + 1)));
+                    issue_pv(1, buf, vp, (uint32_t)j);
+                    umma_commit(kv_empty(vp.slot));
                 }
+                advance2(vp);
+                if (jn < n_b) advance2(kp);
+                if (++buf == NSB) buf = 0, p_par ^= 1u;
+#ifdef DECA_FA_PROFILE
+                m_issue += clock64() - c4;
+#endif
             }
+#ifdef DECA_FA_PROFILE
+            if (blockIdx.x == 0 && blockIdx.y == 0) {
+                g.status->detail[0] = (unsigned)(m_kv / n_b);
+                g.status->detail[1] = (unsigned)(m_pa / n_b);
+                g.status->detail[2] = (unsigned)(m_pb / n_b);
+                g.status->detail[3] = (unsigned)(m_issue / n_b);
+            }
+#endif
             if (!ok) {
                 if (*abort_flag == 0) {
                     *abort_flag = 1;
