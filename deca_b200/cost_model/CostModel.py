@@ -132,13 +132,14 @@ def fa_score(cfg, arch: Arch, shape, causal: bool = False) -> float:
     tile = max(mma, softmax, operands) + handoff
     eff = mma / tile
     # two Q tiles per CTA with P in tensor memory: no P traffic through shared memory and the
-    # MMAs of one tile overlap the softmax of the other (measured +14 % at D = 128, none at D = 64;
+    # MMAs of one tile overlap the softmax of the other (measured +25 % at D = 128 and, against
+    # the one-tile 128-key schedule, +30 % at D = 64, which is +8 % over the best one-tile config;
     # with P in shared memory the two-tile schedule measured no faster than one tile)
     if getattr(cfg, "p_tmem", False):
         if cfg.q_tiles == 2 and cfg.Bc == 64:
             eff *= 0.6  # two score buffers per tile, but twice the barrier round trips (measured)
         elif cfg.q_tiles == 2:
-            eff *= 1.14 if D >= 128 else 1.0
+            eff *= 1.25 if D >= 128 else 1.30
         else:
             # one tile: the softmax warps are the critical path either way; a small gain at D = 64,
             # a small loss at D = 128 (measured)
@@ -149,8 +150,10 @@ def fa_score(cfg, arch: Arch, shape, causal: bool = False) -> float:
     ctas, _ = fa_occupancy(cfg, arch, D, grid)
     slots = arch.sm_nums * ctas
     wave_eff = grid / (math.ceil(grid / slots) * slots)
-    pipe = 1.0 if cfg.stages >= 2 else 0.93
-    pipe *= 1.0 - 0.01 * max(0, cfg.stages - 2)
+    # ring depth in K/V pairs: the two-tile kernel keeps K and V tiles in one ring
+    depth = cfg.stages / 2.0 if cfg.q_tiles == 2 else float(cfg.stages)
+    pipe = 1.0 if depth >= 2 else (0.93 if depth <= 1 else 0.96)
+    pipe *= 1.0 - 0.01 * max(0.0, depth - 2)
     useful = 1.0
     if causal:
         computed = sum(-(-(i + 1) * cfg.Br // cfg.Bc) * cfg.Bc for i in range(n_q)) * cfg.Br

@@ -358,6 +358,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
 #ifdef DECA_FA_PROFILE
         long long t_wait = 0, t_step = 0, t_sig = 0, t_all = clock64();
+        long long g_fa_prof[4] = {0, 0, 0, 0};
 #endif
         for (int j = 0; j < n_kv; ++j) {
             const int buf = j % NSB;
@@ -387,9 +388,9 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             // P in tensor memory reuses the score buffer that was just filled: free by construction
             auto wait_p = [&]() { return PTMEM || wait_prev(); };
             const bool step_ok = diag ? fa_softmax_step<kBc, D, true, PTMEM>(tSg, tOg, pb, r, col0, row_abs, sl2, j == 0,
-                                                                             m, l, wait_p, wait_prev)
+                                                                             m, l, wait_p, wait_prev DECA_FA_PROF_ARG)
                                       : fa_softmax_step<kBc, D, false, PTMEM>(tSg, tOg, pb, r, col0, row_abs, sl2, j == 0,
-                                                                              m, l, wait_p, wait_prev);
+                                                                              m, l, wait_p, wait_prev DECA_FA_PROF_ARG);
             if (!step_ok) {
                 if (lane == 0 && q == 0) report_detail(g.status, 2 + grp, 8, j);
                 ok = false;
@@ -414,6 +415,8 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             g.status->detail[4 + grp * 4 + 1] = (unsigned)(t_step / n_kv);
             g.status->detail[4 + grp * 4 + 2] = (unsigned)(t_sig / n_kv);
             g.status->detail[4 + grp * 4 + 3] = (unsigned)((clock64() - t_all) / n_kv);
+            if (grp == 1 && g_fa_prof[3] > 0)  // first load, exponential pass, P store
+                for (int i = 0; i < 3; ++i) g.status->detail[8 + i] = (unsigned)(g_fa_prof[i] / g_fa_prof[3]);
         }
 #endif
 

@@ -6,9 +6,10 @@
 // a lazily updated running max: as long as the tile's row max exceeds the running max m by at
 // most 2^8 in the exponent, m is kept (P <= 256 is exact enough in fp16 and everything is
 // normalised by l at the end), so the common case is ONE pass over the scores: exponentials with
-// the old max, the row sum and the tile max together.  Only when some row of the warp grew by
-// more (always on the first tile) the slow path runs: raise m, rescale l and the O accumulator in
-// tensor memory, and redo the exponentials with the new max.
+// the old max, the row sum and the tile max together (with P in tensor memory not even the max:
+// a row sum of at most 2^8 already bounds every probability of the tile).  Only when some row of
+// the warp grew by more (always on the first tile) the slow path runs: raise m, rescale l and the
+// O accumulator in tensor memory, and redo the exponentials with the new max.
 #pragma once
 
 #include <type_traits>
@@ -17,7 +18,18 @@
 
 namespace deca {
 
+#ifdef DECA_FA_PROFILE
+// cycle counters of the instrumented build (per thread): first tensor-memory load, the whole
+// exponential pass (including that load), the P store, number of fast-path tiles
+#define DECA_FA_PROF_PARAM , long long (&g_fa_prof)[4]
+#define DECA_FA_PROF_ARG , g_fa_prof
+#else
+#define DECA_FA_PROF_PARAM
+#define DECA_FA_PROF_ARG
+#endif
+
 constexpr float kFaRescaleThreshold = 8.0f;  // log2 units
+constexpr float kFaSumLimit = 256.0f;        // 2^threshold: bound of a tile's row sum on the fast path
 
 // Exponentials of the row with max term `ms` (= m * sl2): writes P (fp16) into the K-major,
 // 128-byte swizzled shared tile at `p_base` (64-key blocks of 128 rows x 128 bytes) and returns
@@ -79,44 +91,62 @@ __device__ __forceinline__ float fa_exp_tile(uint32_t tS, uint32_t p_base, int r
     return (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
 }
 
+// 32 scores of one row (keys cb0 .. cb0 + 31): adds the exponentials 2^(s * sl2 - ms) of the
+// (masked) scores to the packed sums and packs them to fp16, keys (2i, 2i + 1) in pk[i].
+template <bool MASKED>
+__device__ __forceinline__ void fa_exp_chunk32(const uint32_t (&v)[32], int cb0, int row_abs, uint64_t sl2x2,
+                                               uint64_t nmsx2, uint64_t (&sum2)[2], uint32_t *pk) {
+    using P16 = Pack16<DECA_F16>;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float s0 = __uint_as_float(v[2 * i]), s1 = __uint_as_float(v[2 * i + 1]);
+        if constexpr (MASKED) {
+            if (cb0 + 2 * i > row_abs) s0 = kNegInf;
+            if (cb0 + 2 * i + 1 > row_abs) s1 = kNegInf;
+        }
+        float x0, x1;
+        f32x2_unpack(f32x2_fma(f32x2_pack(s0, s1), sl2x2, nmsx2), x0, x1);
+        const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+        sum2[i & 1] = f32x2_add(sum2[i & 1], f32x2_pack(p0, p1));
+        pk[i] = P16::pack(p0, p1);
+    }
+}
+
 // Fast-path variant for P in tensor memory: the exponentials (with the running max) are packed
 // into registers `pk` and NOT stored, because storing would overwrite the scores that a redo with
 // a raised max still needs; the caller stores them once the warp has voted that no row grew by
-// more than the threshold.  Also folds the (masked) raw scores into `mx`.
+// more than the threshold.  No maximum is tracked: the caller tests the returned row sum instead.
+// The tensor-memory load of the next 32 columns is in flight while the current 32 are processed.
 template <int BC, bool MASKED>
-__device__ __forceinline__ float fa_exp_tile_hold(uint32_t tS, int col0, int row_abs, float sl2, float ms, float &mx,
-                                                  uint32_t (&pk)[BC / 2]) {
-    using P16 = Pack16<DECA_F16>;
-    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-    float max4[4] = {kNegInf, kNegInf, kNegInf, kNegInf};
+__device__ __forceinline__ float fa_exp_tile_hold(uint32_t tS, int col0, int row_abs, float sl2, float ms,
+                                                  uint32_t (&pk)[BC / 2] DECA_FA_PROF_PARAM) {
+    constexpr int kChunks = BC / 32;
+    const uint64_t sl2x2 = f32x2_pack(sl2, sl2), nmsx2 = f32x2_pack(-ms, -ms);
+    uint64_t sum2[2] = {0ull, 0ull};
+    uint32_t v[2][32];
+#ifdef DECA_FA_PROFILE
+    const long long pc0 = clock64();
+#endif
+    tmem_ld_32x32b_x32(tS, v[0]);
+    tmem_ld_wait_regs(v[0]);
+#ifdef DECA_FA_PROFILE
+    g_fa_prof[0] += clock64() - pc0;
+#endif
 #pragma unroll
-    for (int h = 0; h < BC / 64; ++h) {
-        uint32_t v0[32], v1[32];
-        tmem_ld_32x32b_x32(tS + h * 64, v0);
-        tmem_ld_32x32b_x32(tS + h * 64 + 32, v1);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            float s0 = __uint_as_float(v0[2 * i]), s1 = __uint_as_float(v0[2 * i + 1]);
-            float s2 = __uint_as_float(v1[2 * i]), s3 = __uint_as_float(v1[2 * i + 1]);
-            if constexpr (MASKED) {
-                const int cb = col0 + h * 64 + 2 * i;
-                if (cb > row_abs) s0 = kNegInf;
-                if (cb + 1 > row_abs) s1 = kNegInf;
-                if (cb + 32 > row_abs) s2 = kNegInf;
-                if (cb + 33 > row_abs) s3 = kNegInf;
-            }
-            max4[0] = fmaxf(max4[0], s0), max4[1] = fmaxf(max4[1], s1);
-            max4[2] = fmaxf(max4[2], s2), max4[3] = fmaxf(max4[3], s3);
-            const float p0 = ex2_approx(fmaf(s0, sl2, -ms)), p1 = ex2_approx(fmaf(s1, sl2, -ms));
-            const float p2 = ex2_approx(fmaf(s2, sl2, -ms)), p3 = ex2_approx(fmaf(s3, sl2, -ms));
-            sum4[0] += p0, sum4[1] += p1, sum4[2] += p2, sum4[3] += p3;
-            pk[h * 32 + i] = P16::pack(p0, p1);
-            pk[h * 32 + 16 + i] = P16::pack(p2, p3);
-        }
+    for (int c = 0; c < kChunks; ++c) {
+        if (c + 1 < kChunks) tmem_ld_32x32b_x32(tS + (c + 1) * 32, v[(c + 1) & 1]);
+        // chunk c = keys 32c ..: half h = c / 2 of the tile, words (c % 2) * 16 .. of that half
+        fa_exp_chunk32<MASKED>(v[c & 1], col0 + c * 32, row_abs, sl2x2, nmsx2, sum2,
+                               &pk[(c / 2) * 32 + (c % 2) * 16]);
+        if (c + 1 < kChunks) tmem_ld_wait_regs(v[(c + 1) & 1]);
     }
-    mx = fmaxf(fmaxf(max4[0], max4[1]), fmaxf(max4[2], max4[3]));
-    return (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+#ifdef DECA_FA_PROFILE
+    g_fa_prof[1] += clock64() - pc0;
+#endif
+    float a0, a1, b0, b1;
+    f32x2_unpack(sum2[0], a0, a1);
+    f32x2_unpack(sum2[1], b0, b1);
+    return (a0 + a1) + (b0 + b1);
 }
 
 // (masked) row maximum of the tile
@@ -150,18 +180,26 @@ __device__ __forceinline__ float fa_row_max(uint32_t tS, int col0, int row_abs) 
 template <int BC, int D, bool MASKED, bool PTMEM, typename WaitP, typename WaitO>
 __device__ __forceinline__ bool fa_softmax_step(uint32_t tS, uint32_t tO, uint32_t p_base, int r, int col0, int row_abs,
                                                 float sl2, bool first_tile, float &m, float &l, WaitP wait_p_free,
-                                                WaitO wait_o_ready) {
+                                                WaitO wait_o_ready DECA_FA_PROF_PARAM) {
     if (!wait_p_free()) return false;
     float mx, lsum = 0.f;
-    bool have_p = false;
+    bool have_p = false, raise;
     if (first_tile) {
         mx = fa_row_max<BC, MASKED>(tS, col0, row_abs);
+        raise = true;
     } else if constexpr (PTMEM) {
         // fast path, P to tensor memory: hold the packed probabilities until the vote, because
-        // storing them overwrites the scores a redo would need
+        // storing them overwrites the scores a redo would need.  The vote is on the row sum: the
+        // probabilities are positive, so a sum of at most 2^threshold bounds every one of them
+        // (no score grew by more than the threshold) without a max over the scores; a larger sum
+        // sends the warp down the slow path, where the exact maximum is taken and m raised.
         uint32_t pk[BC / 2];
-        lsum = fa_exp_tile_hold<BC, MASKED>(tS, col0, row_abs, sl2, m * sl2, mx, pk);
-        if (!__any_sync(0xFFFFFFFFu, (mx - m) * sl2 > kFaRescaleThreshold)) {
+        lsum = fa_exp_tile_hold<BC, MASKED>(tS, col0, row_abs, sl2, m * sl2, pk DECA_FA_PROF_ARG);
+        const bool slow = __any_sync(0xFFFFFFFFu, !(lsum <= kFaSumLimit)) != 0;
+#ifdef DECA_FA_PROFILE
+        const long long pc1 = clock64();
+#endif
+        if (!slow) {
 #pragma unroll
             for (int h = 0; h < BC / 64; ++h) {
                 uint32_t part[32];
@@ -170,15 +208,22 @@ __device__ __forceinline__ bool fa_softmax_step(uint32_t tS, uint32_t tO, uint32
                 tmem_st_32x32b_x32(p_base + h * 32, part);
             }
             tmem_st_wait();
+#ifdef DECA_FA_PROFILE
+            g_fa_prof[2] += clock64() - pc1;
+            g_fa_prof[3] += 1;
+#endif
             l += lsum;
             return true;
         }
+        mx = fa_row_max<BC, MASKED>(tS, col0, row_abs);
+        raise = true;
     } else {
         // fast path, P to shared memory: exponentials with the running max, tile max on the side
         lsum = fa_exp_tile<BC, MASKED, true, PTMEM>(tS, p_base, r, col0, row_abs, sl2, m * sl2, mx);
         have_p = true;
+        raise = __any_sync(0xFFFFFFFFu, (mx - m) * sl2 > kFaRescaleThreshold) != 0;
     }
-    if (__any_sync(0xFFFFFFFFu, (mx - m) * sl2 > kFaRescaleThreshold)) {
+    if (raise) {
         // raise the max, rescale l and O; exponentials computed with the old max are redone
         const float m_new = fmaxf(m, mx);
         const float alpha = ex2_approx((m - m_new) * sl2);

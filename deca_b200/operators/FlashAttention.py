@@ -43,13 +43,14 @@ class FlashAttention(Operator):
         return build_flash_attn(mod)
 
     def default_config(self) -> FAConfig:
-        # measured on B200 over the FlashAttention-2 grid: at D = 128 two Q tiles per CTA with P in
-        # tensor memory win (0.97 PFLOPS at S = 4096); at D = 64 one Q tile, 64-key tiles, P in
-        # tensor memory (0.53-0.56 PFLOPS)
-        if self.D == 64 and self.S_kv % 64 == 0:
-            return FAConfig(Bc=64, stages=2, p_tmem=True)
+        # measured on B200 over the FlashAttention-2 grid: two Q tiles per CTA with 128-key tiles and
+        # P in tensor memory win at both head dims (S = 4096: 1.09 PFLOPS at D = 128, 0.58 at D = 64);
+        # shapes that schedule cannot tile fall back to one Q tile (D = 64: 64-key tiles, P in
+        # tensor memory, 0.54 PFLOPS)
         if self.S_q % 256 == 0 and self.S_kv % 128 == 0:
             return FAConfig(Bc=128, stages=4 if self.S_kv >= 512 else 2, q_tiles=2, p_tmem=True)
+        if self.D == 64 and self.S_kv % 64 == 0:
+            return FAConfig(Bc=64, stages=2, p_tmem=True)
         if self.S_kv % 128 == 0:
             return FAConfig(Bc=128, stages=2)
         return FAConfig(Bc=64, stages=2)

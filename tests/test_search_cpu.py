@@ -49,9 +49,12 @@ def test_every_attention_solution_is_valid(arch):
             if causal and shape[2] != shape[3]:
                 continue
             assert rank_fa_configs(cfgs, arch, shape, causal)[0] in cfgs
-    # measured on B200: 128-key tiles win at D = 128, 64-key tiles at D = 64
-    assert rank_fa_configs(solve_flash_attn(arch, 4, 16, 4096, 4096, 128), arch, (4, 16, 4096, 4096, 128))[0].Bc == 128
-    assert rank_fa_configs(solve_flash_attn(arch, 4, 16, 4096, 4096, 64), arch, (4, 16, 4096, 4096, 64))[0].Bc == 64
+    # measured on B200: two Q tiles per CTA, 128-key tiles, P in tensor memory win at both head dims
+    for d in (128, 64):
+        best = rank_fa_configs(solve_flash_attn(arch, 4, 16, 4096, 4096, d), arch, (4, 16, 4096, 4096, d))[0]
+        assert (best.Bc, best.q_tiles, best.p_tmem, best.stages) == (128, 2, True, 4), best
+    # a 128-row problem cannot use the two-tile schedule
+    assert rank_fa_configs(solve_flash_attn(arch, 1, 1, 128, 128, 64), arch, (1, 1, 128, 128, 64))[0].q_tiles == 1
 
 
 def test_every_rowwise_solution_is_valid(arch):
