@@ -393,6 +393,81 @@ class GemmShardedWorkload(GemmWorkload):
     seed = 4
 
 
+class GemmGatherWorkload(GemmShardedWorkload):
+    """The M-split GEMM followed by the all-gather of C, fused: the kernel's epilogue stores
+    every output panel into all ranks' copies of the gathered C (peer stores over NVLink, no
+    separate collective).  `comparison` in the output line times the unfused form (the same
+    kernel into a local shard, then an NCCL all-gather) in the same process."""
+
+    name = "fp16 GEMM M=65536 N=8192 K=8192 split along M, C all-gathered by the epilogue"
+
+    def __init__(self, rank: int, world: int = 1):
+        import torch
+
+        from deca_b200.sharding import GatheredOutput
+
+        super().__init__(rank, world)
+        self.rank, self.world = rank, world
+        a, b, c = self.dev[0]
+        if world > 1:
+            self.out = GatheredOutput.symmetric(self.M, self.N, torch.float16, a.device)
+        else:
+            self.out = GatheredOutput.from_tensors([c], 0)
+        self.dominant = ("gemm16 + peer stores", str(self.cfg))
+        self.config["gather"] = f"epilogue TMA stores into {world} copies of C[{world * self.M},{self.N}]"
+        self.config["nvlink_bytes_per_step"] = (world - 1) * self.M * self.N * 2
+
+    def step(self):
+        from deca_b200.sharding import gemm_gather
+
+        a, b, _ = self.dev[0]
+        gemm_gather(a, b, self.out, self.cfg)
+
+    dominant_launch = step
+
+    def step_e2e(self):
+        from deca_b200.sharding import gemm_gather
+
+        ha, hb, hc = self.host
+        a, b, _ = self.dev[0]
+        a.copy_(ha, non_blocking=True)
+        b.copy_(hb, non_blocking=True)
+        gemm_gather(a, b, self.out, self.cfg)
+        mine = self.out.local[self.rank * self.M : (self.rank + 1) * self.M]
+        hc.copy_(mine, non_blocking=True)
+        return (ha.numel() + hb.numel()) * 2, hc.numel() * 2
+
+    def comparison(self, steps, barrier):
+        """Unfused: GEMM into a local shard, then all_gather_into_tensor (NCCL); max over ranks."""
+        import torch
+        import torch.distributed as dist
+
+        if self.world == 1:
+            return None
+        a, b, c = self.dev[0]
+        full = torch.empty(self.world * self.M, self.N, dtype=torch.float16, device=a.device)
+
+        def once():
+            self.main(a, b, c)
+            dist.all_gather_into_tensor(full, c)
+
+        for _ in range(3):
+            once()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            once()
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item()) / steps
+        return {"what": "same GEMM kernel into a local shard + NCCL all_gather_into_tensor", "ms_per_step": ms,
+                "value": self.to_value(self.units_per_step * self.world / (ms / 1e3)), "unit": self.unit}
+
+
 class AttentionWorkload:
     """FlashAttention forward fp16, Q, K, V ~ N(0, 1) (seed 3).  One step = the non-causal and
     the causal kernel, each on its own buffer set."""
@@ -667,6 +742,8 @@ def main():
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_value = wl.to_value(wl.units_per_step * args.e2e_steps * world / (float(te.item()) / 1e3))
 
+    comparison = wl.comparison(min(args.steps, 20), barrier) if hasattr(wl, "comparison") else None
+
     if rank == 0:
         clocks = clk.summary()
         achieved = wl.roofline_value(wl.dominant_units / (dom_avg_ms / 1e3))
@@ -686,6 +763,8 @@ def main():
                          "avg_launch_us": dom_avg_ms * 1e3, "traffic": NCU_TRAFFIC_BYTES.get(wl.traffic_key)},
             "clocks": clocks, "clocks_ok": clock_summary_ok(clocks),
         }
+        if comparison is not None:
+            line["comparison"] = comparison
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"], _ = run_cpu_arm(wl, 1, 0, False, world)
         print(json.dumps(line), flush=True)
@@ -695,7 +774,8 @@ def main():
 
 
 WORKLOADS = {"rowwise": RowwiseWorkload, "gemm": GemmWorkload, "attention": AttentionWorkload,
-             "gemm_sharded": GemmShardedWorkload, "attention_sharded": AttentionShardedWorkload}
+             "gemm_sharded": GemmShardedWorkload, "attention_sharded": AttentionShardedWorkload,
+             "gemm_gather": GemmGatherWorkload}
 
 if __name__ == "__main__":
     main()

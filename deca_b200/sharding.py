@@ -4,7 +4,10 @@ The reference is single-GPU (its scripts always use device 0).  The operators sh
 any exchange inside the computation: GEMM along M (B replicated), attention along B*H,
 row-wise operators along rows.  Each rank runs the unchanged single-GPU kernel on its shard;
 the only collective is an optional all-gather of the outputs afterwards
-(``torch.distributed``: NCCL on GPUs, gloo in the CPU tests).
+(``torch.distributed``: NCCL on GPUs, gloo in the CPU tests).  For the M-sharded GEMM that
+all-gather can instead be fused into the kernel: ``GatheredOutput`` holds every rank's copy of
+the gathered C in peer-addressable memory and ``gemm_gather`` has the epilogue store each
+output panel into all of them over NVLink (``deca_gemm16_gather``).
 """
 
 from __future__ import annotations
@@ -75,3 +78,86 @@ def all_gather_rows(local, total_rows: int, group=None):
     parts = [torch.empty_like(buf) for _ in range(world)]
     dist.all_gather(parts, buf, group=group)
     return torch.cat([p[:n] for p, n in zip(parts, sizes)], dim=0)
+
+
+class GatheredOutput:
+    """Every rank's copy of a gathered [world * rows_per_rank, cols] output, addressable from
+    this process: ``local`` is this rank's copy (a tensor), ``ptrs[r]`` the device address of
+    rank r's copy.
+
+    ``GatheredOutput.symmetric`` allocates the copies in torch symmetric memory (one rendezvous
+    over the process group; multicast binding is switched off, the kernel uses plain peer
+    stores).  ``GatheredOutput.from_tensors`` wraps tensors that already live in one process,
+    which is how several ranks are emulated on a single GPU."""
+
+    def __init__(self, local, ptrs, rank: int, rows_per_rank: int, handle=None):
+        self.local = local
+        self.ptrs = [int(p) for p in ptrs]
+        self.rank = rank
+        self.world = len(self.ptrs)
+        self.rows_per_rank = rows_per_rank
+        self._handle = handle  # keeps the symmetric-memory mapping alive
+        if local.data_ptr() != self.ptrs[rank]:
+            raise ValueError("ptrs[rank] is not the local buffer")
+        if local.shape[0] != self.world * rows_per_rank:
+            raise ValueError(f"buffer holds {local.shape[0]} rows, expected {self.world} x {rows_per_rank}")
+
+    @classmethod
+    def symmetric(cls, rows_per_rank: int, cols: int, dtype, device, group=None):
+        import os
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        group = group if group is not None else dist.group.WORLD
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        local = symm_mem.empty((world * rows_per_rank, cols), dtype=dtype, device=device)
+        handle = symm_mem.rendezvous(local, group)
+        return cls(local, list(handle.buffer_ptrs), rank, rows_per_rank, handle)
+
+    @classmethod
+    def from_tensors(cls, copies, rank: int):
+        rows = copies[rank].shape[0]
+        if rows % len(copies) != 0:
+            raise ValueError(f"{rows} rows do not split over {len(copies)} ranks")
+        for t in copies:
+            if t.shape != copies[rank].shape or t.dtype != copies[rank].dtype or not t.is_contiguous():
+                raise ValueError("the copies must be contiguous tensors of one shape and dtype")
+        return cls(copies[rank], [t.data_ptr() for t in copies], rank, rows // len(copies))
+
+    def barrier(self, group=None):
+        """All ranks' kernels launched so far have completed (device-wide on each rank), so
+        every copy holds every shard.  Host-synchronising; outside timed regions."""
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.synchronize(self.local.device)
+        if dist.is_available() and dist.is_initialized():
+            dist.barrier(group=group)
+
+
+def gemm_gather(a_shard, b, out: GatheredOutput, cfg=None):
+    """C_shard = a_shard @ b, stored by the kernel's epilogue into this rank's rows of every
+    copy in ``out`` (see ``deca_gemm16_gather``).  Launches on the current stream and returns
+    without synchronising; call ``out.barrier()`` before reading a gathered copy."""
+    import ctypes
+
+    import torch
+
+    from . import native
+    from .kernels.gemm_b200 import native_cfg
+
+    m, k = a_shard.shape
+    n = b.shape[1]
+    if m != out.rows_per_rank or out.local.shape[1] != n or b.shape[0] != k:
+        raise ValueError(f"shapes do not match: A {tuple(a_shard.shape)}, B {tuple(b.shape)}, "
+                         f"gathered {tuple(out.local.shape)} over {out.world} ranks")
+    if not (a_shard.is_contiguous() and b.is_contiguous()):
+        raise ValueError("A shard and B must be contiguous")
+    ptrs = (ctypes.c_void_p * out.world)(*out.ptrs)
+    ncfg = native_cfg(cfg) if cfg is not None else None
+    rc = native.lib().deca_gemm16_gather(
+        native.DTYPE_CODE[str(a_shard.dtype).replace("torch.", "")], a_shard.data_ptr(), b.data_ptr(), ptrs, out.world, out.rank, m, n, k,
+        ctypes.byref(ncfg) if ncfg is not None else None, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    native.check(rc, "deca_gemm16_gather")
