@@ -1,7 +1,7 @@
 """Benchmark of the hot path on B200: one JSON line per run.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload rowwise|gemm|attention]
-                    [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload rowwise|gemm|attention|gemm_sharded|attention_sharded|gemm_gather]
 
 Default workload ``rowwise``: X[16384, 4096] ~ 3*N(0,1) (seed 1), W ~ N(1, 0.1), eps 1e-6.
 One step = softmax and RMSNorm, each in fp16 and in bf16 (4 kernel launches,
@@ -17,7 +17,10 @@ host cores on a bounded sample.  ``--impl reference`` times only that CPU arm.
 
 Multi-GPU (torchrun, one rank per GPU): every rank runs the same per-GPU workload on its
 own shard (weak scaling: row-wise shards rows, GEMM shards M, attention shards B*H); there
-is no data-path collective; time is the max over ranks.
+is no data-path collective; time is the max over ranks.  ``gemm_sharded`` and
+``attention_sharded`` split one fixed problem instead (strong scaling); ``gemm_gather`` is the
+M-split GEMM whose epilogue also stores C into every rank's copy (the all-gather fused into the
+kernel), with the unfused form (GEMM, then NCCL all-gather) timed beside it in ``comparison``.
 """
 
 from __future__ import annotations
