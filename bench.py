@@ -299,6 +299,7 @@ class GemmWorkload:
     sets = 4
     shard_m = False
     seed = 2
+    tile_override = None
 
     def __init__(self, rank: int, world: int = 1):
         import torch
@@ -312,6 +313,12 @@ class GemmWorkload:
         self.M, self.N, self.K = M, N, K
         self.op = GEMMTC(M, N, K)
         self.cfg = self.op.default_config()
+        if self.tile_override:  # --gemm-tile BMxBN:stages:acc_bufs
+            from deca_b200.kernels.gemm_b200 import GemmConfig
+
+            tile, stages, acc = self.tile_override.split(":")
+            bm, bn = (int(v) for v in tile.split("x"))
+            self.cfg = GemmConfig(BM=bm, BN=bn, stages=int(stages), raster=self.cfg.raster, acc_bufs=int(acc), epi_smem=True)
         self.main = self.op.compile(self.op.build_mod(self.cfg))["main"]
         g = torch.Generator(device="cpu").manual_seed(self.seed + 1000 * rank)
         self.host, self.dev = [], []
@@ -625,6 +632,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-graph", action="store_true", help="launch from Python instead of replaying a CUDA graph")
+    ap.add_argument("--gemm-tile", default=None, help="GEMM workloads: BMxBN:stages:acc_bufs instead of the default config")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -663,6 +671,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.gemm_tile:
+        GemmWorkload.tile_override = args.gemm_tile
     wl = WORKLOADS[args.workload](rank, world)
     peaks = measured_peaks()
 
