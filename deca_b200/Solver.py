@@ -34,7 +34,7 @@ def solve_gemm_tc(arch, M: int, N: int, K: int, type_size: int = 2, count: int =
     accepted for call-site compatibility; the tcgen05 kernel accumulates in fp32 only, so asking
     for fp16 accumulation yields no config.
     """
-    from .kernels.gemm_b200 import SMEM_RESERVED, GemmConfig, check_config
+    from .kernels.gemm_b200 import SMEM_RESERVED, GemmConfig, check_config, stream_k_plan
 
     if acc_f16:
         return []
@@ -72,6 +72,13 @@ def solve_gemm_tc(arch, M: int, N: int, K: int, type_size: int = 2, count: int =
             except AssertionError:
                 continue
             results.append(cfg)
+            # the stream-K form of the config, where whole tiles would leave a quarter of a wave idle
+            tiles = gm_of[vals[0]] * -(-N // vals[1])
+            sms = arch.sm_nums
+            if ras == 8 and cfg.epi_smem and tiles / (-(-tiles // sms) * sms) < 0.75:
+                sk = GemmConfig(**{**cfg.as_dict(), "stream_k": True})
+                if stream_k_plan(sk, M, N, K, sms) is not None:
+                    results.append(sk)
     return results[:count]
 
 

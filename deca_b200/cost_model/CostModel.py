@@ -71,6 +71,18 @@ def gemm_tc_score(cfg, arch: Arch, M: int, N: int, K: int) -> float:
 
     waves = math.ceil(tiles / sm)
     wave_eff = tiles / (waves * sm)
+    if getattr(cfg, "stream_k", False):
+        from ..kernels.gemm_b200 import stream_k_plan
+
+        plan = stream_k_plan(cfg, M, N, K, sm)
+        if plan is not None:
+            # equal shares per SM remove the wave tail, but the CTAs then walk k out of step and
+            # the operand reads lose their reuse in time (0.85), and every CTA writes one partial
+            # tile and reads another, worth about 16 k blocks of its time; fitted to 4096^3
+            # (1219 against 1400 TFLOPS whole-tile) and 2048^3 (440 against 610)
+            grid, dp_tiles, sk_units = plan
+            share = dp_tiles / grid * math.ceil(K / cfg.BK) + sk_units / grid
+            wave_eff = 0.85 * share / (share + 16.0)
     useful = (M * N) / (GM * cfg.BM * GN * cfg.BN)  # partial tiles compute zero-filled rows / columns
 
     # bytes in flight per SM needed to cover ~1 us of L2 latency at the MMA's consumption rate

@@ -32,6 +32,7 @@ class GemmConfig:
     epi_smem: bool = True  # stage C through shared memory and write it with TMA stores
     cta_group: int = 1  # 2: two CTAs of a cluster share one 256-row MMA tile
     acc_bufs: int = 2  # tensor-memory accumulator buffers
+    stream_k: bool = False  # cut the k blocks of the last tiles into one equal share per SM
 
     @property
     def threads(self) -> int:
@@ -44,6 +45,7 @@ class GemmConfig:
         return (
             f"{self.BM}x{self.BN}x{self.BK},cta={self.cta_group},stages={self.stages},"
             f"raster={self.raster},epi_smem={int(self.epi_smem)},acc={self.acc_bufs}"
+            + (",sk=1" if self.stream_k else "")
         )
 
 
@@ -127,7 +129,26 @@ def native_cfg(cfg: GemmConfig):
     from .. import native
 
     return native.GemmCfg(cfg.BM, cfg.BN, cfg.BK, cfg.stages, cfg.raster, int(cfg.epi_smem), cfg.cta_group,
-                          cfg.acc_bufs)
+                          cfg.acc_bufs, int(cfg.stream_k))
+
+
+def stream_k_plan(cfg: GemmConfig, M: int, N: int, K: int, sms: int = 148):
+    """(grid, whole tiles, split units) of the stream-K mode for this shape, or None where the
+    native library would not split (mirror of plan_stream_k in csrc/gemm_f16.cu)."""
+    tiles = -(-M // cfg.BM) * -(-N // cfg.BN)
+    num_kb = -(-K // cfg.BK)
+    waves = -(-tiles // sms)
+    if sms < 2 or tiles / (waves * sms) >= 0.95:
+        return None
+    if tiles >= sms:
+        dp_tiles = (tiles // sms - 1) * sms
+        grid = sms
+    else:
+        dp_tiles = 0
+        grid = min(sms, tiles * num_kb // 8)
+        if grid <= tiles:
+            return None
+    return grid, dp_tiles, (tiles - dp_tiles) * num_kb
 
 
 def bind(spec: KernelSpec):
@@ -147,13 +168,34 @@ def bind(spec: KernelSpec):
     tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[spec.dtype]
     cfg_ref = ctypes.byref(ccfg)
     fn = L.deca_gemm16
+    ws_bytes = ctypes.c_size_t(0)
+    if cfg.stream_k:
+        native.check(L.deca_gemm16_workspace_bytes(dt_code, M, N, K, cfg_ref, ctypes.byref(ws_bytes)),
+                     "deca_gemm16_workspace_bytes")
+    if ws_bytes.value == 0:
 
-    def main(a, b, c):
-        _check_tensor(a, (M, K), tdt, "a")
-        _check_tensor(b, (K, N), tdt, "b")
-        _check_tensor(c, (M, N), tdt, "c")
-        native.check(fn(dt_code, a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, cfg_ref,
-                        current_stream_ptr()), "deca_gemm16")
+        def main(a, b, c):
+            _check_tensor(a, (M, K), tdt, "a")
+            _check_tensor(b, (K, N), tdt, "b")
+            _check_tensor(c, (M, N), tdt, "c")
+            native.check(fn(dt_code, a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, cfg_ref,
+                            current_stream_ptr()), "deca_gemm16")
+
+        if cfg.stream_k:  # nothing to split for this shape: the plain entry point, whole tiles
+            ccfg.stream_k = 0
+    else:
+        # scratch memory of the stream-K mode: zero once, owned by this module, one launch at a time
+        state = {}
+
+        def main(a, b, c):
+            _check_tensor(a, (M, K), tdt, "a")
+            _check_tensor(b, (K, N), tdt, "b")
+            _check_tensor(c, (M, N), tdt, "c")
+            ws = state.get(a.device)
+            if ws is None:
+                ws = state[a.device] = torch.zeros(ws_bytes.value, dtype=torch.uint8, device=a.device)
+            native.check(L.deca_gemm16_ws(dt_code, a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, cfg_ref,
+                                          ws.data_ptr(), ws_bytes.value, current_stream_ptr()), "deca_gemm16_ws")
 
     main._keepalive = ccfg
     return main

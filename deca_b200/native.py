@@ -40,7 +40,8 @@ class RowCfg(ctypes.Structure):
 
 
 class GemmCfg(ctypes.Structure):
-    _fields_ = [(n, ctypes.c_int) for n in ("BM", "BN", "BK", "stages", "raster", "epi_smem", "cta_group", "acc_bufs")]
+    _fields_ = [(n, ctypes.c_int) for n in ("BM", "BN", "BK", "stages", "raster", "epi_smem", "cta_group", "acc_bufs",
+                                            "stream_k")]
 
 
 class FaCfg(ctypes.Structure):
@@ -66,6 +67,8 @@ def lib() -> ctypes.CDLL:
         L.deca_rowwise_default_config.argtypes = [ci, ci, i64, i64, ctypes.POINTER(RowCfg)]
         L.deca_gemm16_check_config.argtypes = [ci, i64, i64, i64, ctypes.POINTER(GemmCfg)]
         L.deca_gemm16.argtypes = [ci, vp, vp, vp, i64, i64, i64, ctypes.POINTER(GemmCfg), vp]
+        L.deca_gemm16_workspace_bytes.argtypes = [ci, i64, i64, i64, ctypes.POINTER(GemmCfg), ctypes.POINTER(ctypes.c_size_t)]
+        L.deca_gemm16_ws.argtypes = [ci, vp, vp, vp, i64, i64, i64, ctypes.POINTER(GemmCfg), vp, ctypes.c_size_t, vp]
         L.deca_gemm16_gather.argtypes = [ci, vp, vp, ctypes.POINTER(vp), ci, ci, i64, i64, i64, ctypes.POINTER(GemmCfg), vp]
         L.deca_fa_fwd_f16_check_config.argtypes = [ci, ci, ci, ci, ci, ci, ctypes.POINTER(FaCfg)]
         L.deca_fa_fwd_f16.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, ctypes.POINTER(FaCfg), vp]

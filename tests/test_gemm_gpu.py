@@ -142,3 +142,100 @@ def test_argument_errors(native):
     bad = native.GemmCfg(128, 256, 64, 8, 8, 1, 1, 2)  # 8 stages of 48 KB do not fit shared memory
     assert L.deca_gemm16(0, a.data_ptr(), b.data_ptr(), c.data_ptr(), 128, 64, 64, ctypes.byref(bad), st) == -4
     torch.cuda.synchronize()
+
+
+# ---------------------------------------------------------------------------- stream-K mode
+def run_stream_k(native, dtype, a, b, cfg_tuple, launches=2):
+    """C through deca_gemm16_ws with stream_k = 1; the same zeroed workspace serves every launch."""
+    M, K = a.shape
+    N = b.shape[1]
+    BM, BN, stages, raster, acc = cfg_tuple
+    ccfg = native.GemmCfg(BM, BN, 64, stages, raster, 1, 1, acc, 1)
+    L = native.lib()
+    nbytes = ctypes.c_size_t(0)
+    assert L.deca_gemm16_workspace_bytes(native.DTYPE_CODE[dtype], M, N, K, ctypes.byref(ccfg), ctypes.byref(nbytes)) == 0
+    ws = torch.zeros(max(nbytes.value, 256), dtype=torch.uint8, device="cuda")
+    outs = []
+    for _ in range(launches):
+        buf = torch.full((M + 2, N), 7.0, dtype=a.dtype, device="cuda")
+        c = buf[1 : M + 1]
+        st = L.deca_gemm16_ws(native.DTYPE_CODE[dtype], a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, ctypes.byref(ccfg),
+                              ws.data_ptr(), nbytes.value, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert st == 0, native.status_string(st)
+        assert native.last_device_status() == (0, 0, 0)
+        assert torch.all(buf[0] == 7.0) and torch.all(buf[M + 1] == 7.0), "canary rows overwritten"
+        outs.append(torch_to_bits(c))
+    if nbytes.value:
+        flags = ws[: 148 * 16].view(torch.int32)
+        assert int(flags.abs().sum().item()) == 0, "ready flags not cleared by the launch"
+    return outs, nbytes.value
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape,cfg", [
+    ((4096, 4096, 512), (256, 256, 3, 8, 1)),    # 256 tiles on 148 SMs: every tile in the split region
+    ((2048, 2048, 1024), (128, 256, 4, 8, 2)),   # 128 tiles: fewer tiles than SMs, 16 k blocks each
+    ((1280, 1280, 1024), (128, 128, 4, 4, 2)),   # 100 tiles
+    ((2560, 2560, 256), (128, 128, 3, 4, 2)),    # 400 tiles: one whole wave, then 252 tiles split
+    ((1000, 1096, 520), (128, 128, 3, 2, 2)),    # partial tiles in M, N and K
+    ((256, 256, 4096), (128, 128, 4, 1, 2)),     # 4 tiles, 64 k blocks each: many CTAs per tile
+])
+def test_stream_k_matches_oracle_and_plain_kernel(native, dtype, shape, cfg):
+    M, N, K = shape
+    a_bits, b_bits = make_ab(M, N, K, dtype, seed=5)
+    a, b = bits_to_torch(a_bits, dtype), bits_to_torch(b_bits, dtype)
+    outs, nbytes = run_stream_k(native, dtype, a, b, cfg)
+    assert nbytes > 0, "the shape was meant to be split"
+    assert np.array_equal(outs[0], outs[1]), "two launches on one workspace differ"
+    check(dtype, a_bits, b_bits, outs[0])
+    BM, BN, stages, raster, acc = cfg
+    plain = run_native(native, dtype, a_bits, b_bits, dict(BM=BM, BN=BN, stages=stages, raster=raster, acc_bufs=acc))
+    # split tiles are summed in another order in fp32: after rounding to 16 bits nearly all agree
+    assert np.mean(plain == outs[0]) > 0.98
+
+
+def test_stream_k_not_applied_and_argument_errors(native):
+    L = native.lib()
+    ccfg = native.GemmCfg(256, 256, 64, 3, 8, 1, 1, 1, 1)
+    n = ctypes.c_size_t(123)
+    assert L.deca_gemm16_workspace_bytes(native.F16, 8192, 8192, 8192, ctypes.byref(ccfg), ctypes.byref(n)) == 0
+    assert n.value == 0  # 1024 tiles fill 6.9 waves: nothing to split
+    a = torch.zeros(512, 2048, dtype=torch.float16, device="cuda")
+    b = torch.zeros(2048, 512, dtype=torch.float16, device="cuda")
+    c = torch.zeros(512, 512, dtype=torch.float16, device="cuda")
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    small = native.GemmCfg(128, 128, 64, 3, 1, 1, 1, 2, 1)
+    assert L.deca_gemm16(native.F16, a.data_ptr(), b.data_ptr(), c.data_ptr(), 512, 512, 2048, ctypes.byref(small), st) == -4
+    assert L.deca_gemm16_workspace_bytes(native.F16, 512, 512, 512, ctypes.byref(small), ctypes.byref(n)) == 0
+    assert n.value == 0  # 16 tiles of 8 k blocks: too little work per CTA to split
+    assert L.deca_gemm16_workspace_bytes(native.F16, 512, 512, 2048, ctypes.byref(small), ctypes.byref(n)) == 0
+    assert n.value == 256 * 4 + 64 * 128 * 128 * 4  # 64 CTAs: flags (rounded to 256 bytes) + one fp32 tile each
+    ws = torch.zeros(n.value, dtype=torch.uint8, device="cuda")
+    args = (native.F16, a.data_ptr(), b.data_ptr(), c.data_ptr(), 512, 512, 2048, ctypes.byref(small))
+    assert L.deca_gemm16_ws(*args, None, 0, st) == -1
+    assert L.deca_gemm16_ws(*args, ws.data_ptr(), n.value - 1, st) == -2
+    assert L.deca_gemm16_ws(*args, ws.data_ptr() + 16, n.value, st) == -3
+    assert L.deca_gemm16_ws(*args, ws.data_ptr(), n.value, st) == 0
+    bad = native.GemmCfg(128, 128, 64, 3, 1, 1, 1, 2, 2)
+    assert L.deca_gemm16_check_config(native.F16, 512, 512, 512, ctypes.byref(bad)) == -4
+    torch.cuda.synchronize()
+    assert native.last_device_status() == (0, 0, 0)
+
+
+def test_stream_k_through_the_operator(native):
+    from deca_b200.kernels.gemm_b200 import GemmConfig, stream_k_plan
+    from deca_b200.operators import GEMMTC
+
+    op = GEMMTC(2048, 2048, 2048)
+    cfg = GemmConfig(BM=256, BN=256, stages=3, raster=8, acc_bufs=1, stream_k=True)
+    assert stream_k_plan(cfg, 2048, 2048, 2048) == (148, 0, 64 * 32)
+    a, b = op.make_inputs()
+    ref = op.reference((a, b))
+    out = op(a, b, cfg=cfg)
+    out2 = op(a, b, cfg=cfg)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+    atol, rtol = op.tolerance
+    assert torch.allclose(out.float(), ref.float(), atol=atol, rtol=rtol)
+    assert native.last_device_status() == (0, 0, 0)
