@@ -61,6 +61,7 @@ extern "C" const char *deca_status_string(int status) {
         case DECA_ERR_ALIGN: return "pointer or pitch is not aligned for this kernel";
         case DECA_ERR_CONFIG: return "kernel config rejected";
         case DECA_ERR_UNSUPPORTED: return "op, dtype or mode not built";
+        case DECA_ERR_SCRATCH_LIMIT: return "the problem needs more scratch memory than the built-in buffer holds";
         case DECA_ERR_DEVICE_TIMEOUT: return "a kernel gave up on a bounded wait";
     }
     if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));

@@ -69,6 +69,7 @@ def lib() -> ctypes.CDLL:
         L.deca_gemm16.argtypes = [ci, vp, vp, vp, i64, i64, i64, ctypes.POINTER(GemmCfg), vp]
         L.deca_gemm16_workspace_bytes.argtypes = [ci, i64, i64, i64, ctypes.POINTER(GemmCfg), ctypes.POINTER(ctypes.c_size_t)]
         L.deca_gemm16_ws.argtypes = [ci, vp, vp, vp, i64, i64, i64, ctypes.POINTER(GemmCfg), vp, ctypes.c_size_t, vp]
+        L.deca_gemm16_sk_static.argtypes = [ci, vp, vp, vp, i64, i64, i64, ctypes.POINTER(GemmCfg), vp]
         L.deca_gemm16_gather.argtypes = [ci, vp, vp, ctypes.POINTER(vp), ci, ci, i64, i64, i64, ctypes.POINTER(GemmCfg), vp]
         L.deca_fa_fwd_f16_check_config.argtypes = [ci, ci, ci, ci, ci, ci, ctypes.POINTER(FaCfg)]
         L.deca_fa_fwd_f16.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, ctypes.POINTER(FaCfg), vp]
