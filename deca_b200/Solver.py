@@ -79,6 +79,19 @@ def solve_gemm_tc(arch, M: int, N: int, K: int, type_size: int = 2, count: int =
                 sk = GemmConfig(**{**cfg.as_dict(), "stream_k": True})
                 if stream_k_plan(sk, M, N, K, sms) is not None:
                     results.append(sk)
+    # CTA pairs (tcgen05 cta_group::2) on a 512 x 256 tile: worth offering once the problem has a
+    # pair tile for half of the SMs
+    if -(-M // 512) * -(-N // 256) >= arch.sm_nums // 4:
+        for st in (3, 4):
+            for ras in (1, 2, 4, 8, 16):
+                if ras > 1 and ras > -(-M // 512):
+                    continue
+                cfg = GemmConfig(BM=256, BN=256, BK=64, stages=st, raster=ras, epi_smem=True, cta_group=2, acc_bufs=1)
+                try:
+                    check_config(cfg, M, N, K)
+                except AssertionError:
+                    continue
+                results.append(cfg)
     return results[:count]
 
 

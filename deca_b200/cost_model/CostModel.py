@@ -58,11 +58,17 @@ def gemm_tc_score(cfg, arch: Arch, M: int, N: int, K: int) -> float:
     halves = cfg.BM // 128
     peak = arch.peak_tcgen05_flops * 1e9
     t_mma = sm / peak
-    smem_bpf = (cfg.BM * 32 + halves * cfg.BN * 32) / (2.0 * cfg.BM * cfg.BN * 16)
+    # CTA pairs: each CTA fetches and reads only its half of the B columns, and a tile (2 BM rows)
+    # occupies two SMs
+    pair = getattr(cfg, "cta_group", 1) == 2
+    bn_own = cfg.BN // 2 if pair else cfg.BN
+    smem_bpf = (cfg.BM * 32 + halves * bn_own * 32) / (2.0 * cfg.BM * cfg.BN * 16)
     t_smem = smem_bpf / arch.smem_bw_per_sm
-    l2_bpf = (cfg.BM + cfg.BN) / (cfg.BM * cfg.BN)
+    l2_bpf = (cfg.BM + bn_own) / (cfg.BM * cfg.BN)
     t_l2 = l2_bpf * sm / (arch.l2_bw * 1e9)
     GM, GN = -(-M // cfg.BM), -(-N // cfg.BN)
+    if pair:
+        GM = 2 * -(-M // (2 * cfg.BM))  # rows come in pair tiles
     tiles = GM * GN
     slots = min(sm, tiles)
     t_dram = gemm_wave_dram_bytes_per_flop(cfg, arch, M, N, K, slots) * sm / (arch.dram_bw * 1e9)

@@ -239,3 +239,51 @@ def test_stream_k_through_the_operator(native):
     atol, rtol = op.tolerance
     assert torch.allclose(out.float(), ref.float(), atol=atol, rtol=rtol)
     assert native.last_device_status() == (0, 0, 0)
+
+
+# ---------------------------------------------------------------------------- CTA pairs (cta_group::2)
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape,stages,raster", [
+    ((512, 256, 64), 2, 1),       # one pair tile, one k block
+    ((1024, 512, 512), 3, 2),
+    ((1000, 520, 264), 4, 8),     # partial tiles in M, N and K; the odd CTA's rows partly outside M
+    ((300, 256, 128), 3, 1),      # the odd CTA's 256 rows mostly outside M
+    ((2048, 4096, 1024), 4, 8),   # 64 pair tiles: one wave
+    ((8192, 2048, 256), 3, 4),    # 128 pair tiles: every pair runs more than one tile
+])
+def test_cta_pair_kernel_matches_oracle(native, dtype, shape, stages, raster):
+    M, N, K = shape
+    a_bits, b_bits = make_ab(M, N, K, dtype, seed=7)
+    a, b = bits_to_torch(a_bits, dtype), bits_to_torch(b_bits, dtype)
+    buf = torch.full((M + 2, N), 7.0, dtype=a.dtype, device="cuda")
+    c = buf[1 : M + 1]
+    ccfg = native.GemmCfg(256, 256, 64, stages, raster, 1, 2, 1, 0)
+    L = native.lib()
+    assert L.deca_gemm16_check_config(native.DTYPE_CODE[dtype], M, N, K, ctypes.byref(ccfg)) == 0
+    for _ in range(2):
+        st = L.deca_gemm16(native.DTYPE_CODE[dtype], a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, ctypes.byref(ccfg),
+                           ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert st == 0, native.status_string(st)
+    torch.cuda.synchronize()
+    assert native.last_device_status() == (0, 0, 0)
+    assert torch.all(buf[0] == 7.0) and torch.all(buf[M + 1] == 7.0), "canary rows overwritten"
+    got = torch_to_bits(c)
+    check(dtype, a_bits, b_bits, got)
+    # same k order per element as the one-CTA kernel: identical bits
+    plain = run_native(native, dtype, a_bits, b_bits, dict(BM=256, BN=256, stages=3, raster=raster, acc_bufs=1))
+    assert np.array_equal(got, plain)
+
+
+def test_cta_pair_config_rules(native):
+    L = native.lib()
+
+    def rc(*fields):
+        return L.deca_gemm16_check_config(native.F16, 4096, 4096, 4096, ctypes.byref(native.GemmCfg(*fields)))
+
+    assert rc(256, 256, 64, 4, 8, 1, 2, 1, 0) == 0
+    assert rc(128, 256, 64, 4, 8, 1, 2, 1, 0) == -4  # 256 rows per CTA only
+    assert rc(256, 256, 64, 5, 8, 1, 2, 1, 0) == -4  # five stages do not fit
+    assert rc(256, 256, 64, 3, 8, 0, 2, 1, 0) == -4  # staged epilogue only
+    assert rc(256, 256, 64, 3, 8, 1, 2, 2, 0) == -4  # one accumulator (all 512 columns)
+    assert rc(256, 256, 64, 3, 8, 1, 2, 1, 1) == -4  # no stream-K
+    assert rc(256, 256, 64, 3, 8, 1, 3, 1, 0) == -4
