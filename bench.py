@@ -1,7 +1,7 @@
 """Benchmark of the hot path on B200: one JSON line per run.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload rowwise|gemm|attention|gemm_sharded|attention_sharded|gemm_gather]
+                    [--workload rowwise|gemm|attention|gemm_sharded|attention_sharded|gemm_gather|attention_gather]
 
 Default workload ``rowwise``: X[16384, 4096] ~ 3*N(0,1) (seed 1), W ~ N(1, 0.1), eps 1e-6.
 One step = softmax and RMSNorm, each in fp16 and in bf16 (4 kernel launches,
@@ -18,9 +18,10 @@ host cores on a bounded sample.  ``--impl reference`` times only that CPU arm.
 Multi-GPU (torchrun, one rank per GPU): every rank runs the same per-GPU workload on its
 own shard (weak scaling: row-wise shards rows, GEMM shards M, attention shards B*H); there
 is no data-path collective; time is the max over ranks.  ``gemm_sharded`` and
-``attention_sharded`` split one fixed problem instead (strong scaling); ``gemm_gather`` is the
-M-split GEMM whose epilogue also stores C into every rank's copy (the all-gather fused into the
-kernel), with the unfused form (GEMM, then NCCL all-gather) timed beside it in ``comparison``.
+``attention_sharded`` split one fixed problem instead (strong scaling); ``gemm_gather`` and
+``attention_gather`` are those two with the epilogue also storing the output into every rank's
+copy (the all-gather fused into the kernel), the unfused form (kernel, then NCCL all-gather)
+timed beside it in ``comparison``.
 """
 
 from __future__ import annotations
@@ -588,6 +589,83 @@ class AttentionShardedWorkload(AttentionWorkload):
     seed = 4
 
 
+class AttentionGatherWorkload(AttentionShardedWorkload):
+    """The head-split causal attention followed by the all-gather of O, fused: the kernel's
+    epilogue stores every output panel into all ranks' copies of the gathered O (peer stores over
+    NVLink).  `comparison` times the unfused form (same kernel, then an NCCL all-gather)."""
+
+    name = "FlashAttention fwd fp16 B=32 H=32 S=8192 D=128 causal split along B*H, O all-gathered by the epilogue"
+
+    def __init__(self, rank: int, world: int = 1):
+        import torch
+
+        from deca_b200.sharding import GatheredOutput
+
+        super().__init__(rank, world)
+        self.rank, self.world = rank, world
+        q, k, v, o = self.dev[0]
+        rows = self.B * self.H * self.S
+        if world > 1:
+            self.out = GatheredOutput.symmetric(rows, self.D, torch.float16, q.device)
+        else:
+            self.out = GatheredOutput.from_tensors([o.view(rows, self.D)], 0)
+        self.dominant = ("fa_fwd + peer stores", self.dominant[1])
+        self.config["gather"] = f"epilogue TMA stores into {world} copies of O[{world * self.B * self.H},{self.S},{self.D}]"
+        self.config["nvlink_bytes_per_step"] = (world - 1) * rows * self.D * 2
+
+    def step(self):
+        from deca_b200.sharding import attention_gather
+
+        q, k, v, _ = self.dev[0]
+        attention_gather(q, k, v, self.out, causal=True)
+
+    dominant_launch = step
+
+    def step_e2e(self):
+        from deca_b200.sharding import attention_gather
+
+        hq, hk, hv, ho = self.host
+        q, k, v, _ = self.dev[0]
+        h2d = 0
+        for src, dst in ((hq, q), (hk, k), (hv, v)):
+            dst.copy_(src, non_blocking=True)
+            h2d += src.numel() * 2
+        attention_gather(q, k, v, self.out, causal=True)
+        rows = self.B * self.H * self.S
+        ho.view(rows, self.D).copy_(self.out.local[self.rank * rows : (self.rank + 1) * rows], non_blocking=True)
+        return h2d, ho.numel() * 2
+
+    def comparison(self, steps, barrier):
+        import torch
+        import torch.distributed as dist
+
+        if self.world == 1:
+            return None
+        q, k, v, o = self.dev[0]
+        main = self.ops[0][1]
+        full = torch.empty(self.world * o.numel(), dtype=torch.float16, device=o.device)
+
+        def once():
+            main(q, k, v, o)
+            dist.all_gather_into_tensor(full, o.view(-1))
+
+        for _ in range(3):
+            once()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            once()
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item()) / steps
+        return {"what": "same attention kernel into a local shard + NCCL all_gather_into_tensor", "ms_per_step": ms,
+                "value": self.to_value(self.units_per_step * self.world / (ms / 1e3)), "unit": self.unit}
+
+
 def clock_summary_ok(c):
     bad = {"hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown"}
     return not (bad & set(c.get("reasons", [])))
@@ -788,7 +866,7 @@ def main():
 
 WORKLOADS = {"rowwise": RowwiseWorkload, "gemm": GemmWorkload, "attention": AttentionWorkload,
              "gemm_sharded": GemmShardedWorkload, "attention_sharded": AttentionShardedWorkload,
-             "gemm_gather": GemmGatherWorkload}
+             "gemm_gather": GemmGatherWorkload, "attention_gather": AttentionGatherWorkload}
 
 if __name__ == "__main__":
     main()

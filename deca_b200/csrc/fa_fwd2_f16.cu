@@ -35,6 +35,7 @@ struct Fa2Args {
     int causal;
     int stages;  // K/V ring slots
     float sl2;
+    int n_peers;  // every output panel is also stored through peers.m[0 .. n_peers)
     DeviceStatus *status;
 };
 
@@ -45,7 +46,8 @@ struct Fa2Args {
 template <int D, int BC, bool PTMEM>
 __global__ void __launch_bounds__(kThreads2, 1)
 fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const Fa2Args g) {
+               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+               const __grid_constant__ PeerMaps peers, const Fa2Args g) {
     using P16 = Pack16<DECA_F16>;
     constexpr int kBc = BC;
     constexpr int NSB = (BC == 64) ? 2 : 1;  // score buffers per group
@@ -114,7 +116,14 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         mbar_init(drain_bar, 1);
         fence_barrier_init();
-        prefetch_tensormap(&tmQ);
+        // This thread is also the TMA producer: the Q tiles are requested here, before the CTA's
+        // set-up barrier, so that their latency overlaps the tensor-memory allocation.
+        mbar_arrive_expect_tx(q_full, 2 * kQBytes);
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+            for (int blk = 0; blk < D / 64; ++blk)
+                tma_load_2d(sQ + t * kQBytes + blk * 16384, &tmQ, blk * 64, q_row0 + t * kBr, q_full);
         prefetch_tensormap(&tmK);
         prefetch_tensormap(&tmV);
         prefetch_tensormap(&tmO);
@@ -134,12 +143,6 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             bool ok = true;
-            mbar_arrive_expect_tx(q_full, 2 * kQBytes);
-#pragma unroll
-            for (int t = 0; t < 2; ++t)
-#pragma unroll
-                for (int blk = 0; blk < D / 64; ++blk)
-                    tma_load_2d(sQ + t * kQBytes + blk * 16384, &tmQ, blk * 64, q_row0 + t * kBr, q_full);
             int s = 0;
             uint32_t ph = 0;
             int n_items = 0;
@@ -460,6 +463,11 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
                 for (int blk = 0; blk < D / 64; ++blk)
                     tma_store_2d(&tmO, stage0 + blk * 16384 + q * 4096, blk * 64, q_row0 + grp * kBr + q * 32);
+                // gather: the same rows of O go to the other ranks' copies (plain TMA stores to peer memory)
+                for (int pr = 0; pr < g.n_peers; ++pr)
+#pragma unroll
+                    for (int blk = 0; blk < D / 64; ++blk)
+                        tma_store_2d(&peers.m[pr], stage0 + blk * 16384 + q * 4096, blk * 64, q_row0 + grp * kBr + q * 32);
                 tma_store_commit();
                 tma_store_wait<0>();
             }
@@ -478,6 +486,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
 template <int D, int BC, bool PTMEM>
 int launch_fa2(const CUtensorMap &tmQ, const CUtensorMap &tmK, const CUtensorMap &tmV, const CUtensorMap &tmO,
+               const PeerMaps &peers,
                const Fa2Args &g, dim3 grid, size_t smem, cudaStream_t st) {
     static std::atomic<size_t> configured{0};
     if (configured.load(std::memory_order_relaxed) < smem) {
@@ -485,7 +494,7 @@ int launch_fa2(const CUtensorMap &tmQ, const CUtensorMap &tmK, const CUtensorMap
         if (e != cudaSuccess) return (int)e;
         configured.store(smem, std::memory_order_relaxed);
     }
-    fa_fwd2_kernel<D, BC, PTMEM><<<grid, kThreads2, smem, st>>>(tmQ, tmK, tmV, tmO, g);
+    fa_fwd2_kernel<D, BC, PTMEM><<<grid, kThreads2, smem, st>>>(tmQ, tmK, tmV, tmO, peers, g);
     return (int)cudaGetLastError();
 }
 
@@ -507,10 +516,11 @@ int fa2_check(int S_q, int S_kv, int D, const deca_fa_cfg &c) {
     return DECA_OK;
 }
 
-int fa2_launch(const CUtensorMap &tmQ, const CUtensorMap &tmK, const CUtensorMap &tmV, const CUtensorMap &tmO, int B,
-               int H, int S_q, int S_kv, int D, float softmax_scale, int causal, const deca_fa_cfg &c,
-               cudaStream_t st) {
+int fa2_launch(const CUtensorMap &tmQ, const CUtensorMap &tmK, const CUtensorMap &tmV, const CUtensorMap &tmO,
+               const PeerMaps &peers, int n_peers, int B, int H, int S_q, int S_kv, int D, float softmax_scale, int causal,
+               const deca_fa_cfg &c, cudaStream_t st) {
     Fa2Args g;
+    g.n_peers = n_peers;
     g.S_q = S_q, g.S_kv = S_kv;
     g.causal = causal ? 1 : 0;
     g.stages = c.stages;
@@ -521,13 +531,13 @@ int fa2_launch(const CUtensorMap &tmQ, const CUtensorMap &tmK, const CUtensorMap
     const bool ptmem = c.p_tmem != 0;
     const size_t smem = fa2_smem_bytes(D, c.Bc, c.stages, ptmem);
     if (c.Bc == 64)
-        return D == 128 ? launch_fa2<128, 64, true>(tmQ, tmK, tmV, tmO, g, grid, smem, st)
-                        : launch_fa2<64, 64, true>(tmQ, tmK, tmV, tmO, g, grid, smem, st);
+        return D == 128 ? launch_fa2<128, 64, true>(tmQ, tmK, tmV, tmO, peers, g, grid, smem, st)
+                        : launch_fa2<64, 64, true>(tmQ, tmK, tmV, tmO, peers, g, grid, smem, st);
     if (ptmem)
-        return D == 128 ? launch_fa2<128, 128, true>(tmQ, tmK, tmV, tmO, g, grid, smem, st)
-                        : launch_fa2<64, 128, true>(tmQ, tmK, tmV, tmO, g, grid, smem, st);
-    return D == 128 ? launch_fa2<128, 128, false>(tmQ, tmK, tmV, tmO, g, grid, smem, st)
-                    : launch_fa2<64, 128, false>(tmQ, tmK, tmV, tmO, g, grid, smem, st);
+        return D == 128 ? launch_fa2<128, 128, true>(tmQ, tmK, tmV, tmO, peers, g, grid, smem, st)
+                        : launch_fa2<64, 128, true>(tmQ, tmK, tmV, tmO, peers, g, grid, smem, st);
+    return D == 128 ? launch_fa2<128, 128, false>(tmQ, tmK, tmV, tmO, peers, g, grid, smem, st)
+                    : launch_fa2<64, 128, false>(tmQ, tmK, tmV, tmO, peers, g, grid, smem, st);
 }
 
 }  // namespace deca

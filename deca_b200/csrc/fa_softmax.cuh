@@ -184,10 +184,28 @@ __device__ __forceinline__ bool fa_softmax_step(uint32_t tS, uint32_t tO, uint32
     if (!wait_p_free()) return false;
     float mx, lsum = 0.f;
     bool have_p = false, raise;
-    if (first_tile) {
+    if (first_tile && !PTMEM) {
         mx = fa_row_max<BC, MASKED>(tS, col0, row_abs);
         raise = true;
     } else if constexpr (PTMEM) {
+        if (first_tile) {
+            // nothing accumulated yet (l = 0, O empty): start the running max at the maximum of
+            // the first 32 keys (key 0 is visible to every row) and take the fast path; the rest
+            // of the tile rarely exceeds it by 2^8, and then the slow path below corrects it
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(tS, v);
+            tmem_ld_wait();
+            float part[4] = {kNegInf, kNegInf, kNegInf, kNegInf};
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                float sc = __uint_as_float(v[i]);
+                if constexpr (MASKED) {
+                    if (col0 + i > row_abs) sc = kNegInf;
+                }
+                part[i & 3] = fmaxf(part[i & 3], sc);
+            }
+            m = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
+        }
         // fast path, P to tensor memory: hold the packed probabilities until the vote, because
         // storing them overwrites the scores a redo would need.  The vote is on the row sum: the
         // probabilities are positive, so a sum of at most 2^threshold bounds every one of them

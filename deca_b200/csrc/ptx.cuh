@@ -112,6 +112,14 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
 
+// Tensor maps of the same output region in up to seven further buffers (the other ranks' copies of
+// a gathered output, in peer memory): an epilogue that stores through them as well performs the
+// all-gather.  Only stores go through these maps.
+constexpr int kMaxPeers = 7;
+struct PeerMaps {
+    CUtensorMap m[kMaxPeers];
+};
+
 // ---------------------------------------------------------------- tensor memory
 // Executed by one full warp.  The base address of the allocation is written to `smem_slot`.
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {

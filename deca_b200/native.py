@@ -73,6 +73,8 @@ def lib() -> ctypes.CDLL:
         L.deca_gemm16_gather.argtypes = [ci, vp, vp, ctypes.POINTER(vp), ci, ci, i64, i64, i64, ctypes.POINTER(GemmCfg), vp]
         L.deca_fa_fwd_f16_check_config.argtypes = [ci, ci, ci, ci, ci, ci, ctypes.POINTER(FaCfg)]
         L.deca_fa_fwd_f16.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, ctypes.POINTER(FaCfg), vp]
+        L.deca_fa_fwd_f16_gather.argtypes = [vp, vp, vp, ctypes.POINTER(vp), ci, ci, ci, ci, ci, ci, ci, cf, ci,
+                                             ctypes.POINTER(FaCfg), vp]
         ip = ctypes.POINTER(ci)
         L.deca_last_device_status.argtypes = [ip, ip, ip, ci]
         L.deca_device_status_words.argtypes = [ctypes.POINTER(ctypes.c_uint), ci]

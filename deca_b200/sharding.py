@@ -7,7 +7,8 @@ the only collective is an optional all-gather of the outputs afterwards
 (``torch.distributed``: NCCL on GPUs, gloo in the CPU tests).  For the M-sharded GEMM that
 all-gather can instead be fused into the kernel: ``GatheredOutput`` holds every rank's copy of
 the gathered C in peer-addressable memory and ``gemm_gather`` has the epilogue store each
-output panel into all of them over NVLink (``deca_gemm16_gather``).
+output panel into all of them over NVLink (``deca_gemm16_gather``); ``attention_gather`` does
+the same for the head-sharded attention output (``deca_fa_fwd_f16_gather``).
 """
 
 from __future__ import annotations
@@ -161,3 +162,35 @@ def gemm_gather(a_shard, b, out: GatheredOutput, cfg=None):
         native.DTYPE_CODE[str(a_shard.dtype).replace("torch.", "")], a_shard.data_ptr(), b.data_ptr(), ptrs, out.world, out.rank, m, n, k,
         ctypes.byref(ncfg) if ncfg is not None else None, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     native.check(rc, "deca_gemm16_gather")
+
+
+def attention_gather(q, k, v, out: GatheredOutput, causal: bool = False, softmax_scale=None, cfg=None):
+    """O = attention(q, k, v) for this rank's heads ([B, H, S, D] shards of the flattened B * H
+    axis), stored by the kernel's epilogue into this rank's heads of every copy in ``out``, whose
+    buffers are [world * B * H * S_q, D] (see ``deca_fa_fwd_f16_gather``).  Launches on the
+    current stream without synchronising; call ``out.barrier()`` before reading a gathered copy."""
+    import ctypes
+
+    import torch
+
+    from . import native
+    from .kernels.flash_attn_b200 import native_cfg
+
+    B, H, S_q, D = q.shape
+    S_kv = k.shape[2]
+    if out.rows_per_rank != B * H * S_q or out.local.shape[1] != D:
+        raise ValueError(f"gathered buffer {tuple(out.local.shape)} over {out.world} ranks does not hold "
+                         f"{B * H} heads of {S_q} x {D} per rank")
+    if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()) or q.dtype != torch.float16:
+        raise ValueError("q, k, v must be contiguous float16 tensors")
+    scale = float(softmax_scale) if softmax_scale is not None else D ** -0.5
+    ptrs = (ctypes.c_void_p * out.world)(*out.ptrs)
+    if cfg is None:
+        from .operators import FlashAttention
+
+        cfg = FlashAttention(B, H, S_q, S_kv, D, causal=causal).default_config()
+    ncfg = native_cfg(cfg)
+    rc = native.lib().deca_fa_fwd_f16_gather(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), ptrs, out.world, out.rank, B, H, S_q, S_kv, D, ctypes.c_float(scale),
+        int(causal), ctypes.byref(ncfg), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    native.check(rc, "deca_fa_fwd_f16_gather")

@@ -1,4 +1,4 @@
-"""The fused GEMM + all-gather across real GPUs: one process per GPU, the gathered output in
+"""The fused GEMM + all-gather (and attention + all-gather) across real GPUs: one process per GPU, the gathered output in
 torch symmetric memory, peer stores over NVLink.  Needs at least two GPUs (skipped otherwise;
 the single-GPU emulation of the same path is in test_gemm_gather_gpu.py).  No rank leaves
 early and no kernel waits on a peer: the only cross-rank synchronisation is the host barrier
@@ -48,6 +48,24 @@ def _worker(rank: int, world: int, port: int, m_shard: int, n: int, k: int):
         torch.cuda.synchronize()
         assert torch.equal(out.local, want), f"rank {rank}: gathered copy differs from the unsharded result"
         out.barrier()
+
+        # attention: two heads per rank, O gathered by the epilogue
+        from deca_b200.operators import FlashAttention
+        from deca_b200.sharding import attention_gather, shard_attention
+
+        heads, S, D = 2 * world, 512, 128
+        q, k, v = (torch.randn(1, heads, S, D, generator=g).half().cuda() for _ in range(3))
+        o_all = GatheredOutput.symmetric(2 * S, D, torch.float16, q.device)
+        o_all.local.fill_(7.0)
+        o_all.barrier()
+        qs, ks, vs, _ = shard_attention(q, k, v, rank, world)
+        attention_gather(qs.contiguous(), ks.contiguous(), vs.contiguous(), o_all, causal=True)
+        o_all.barrier()
+        assert native.last_device_status() == (0, 0, 0)
+        want_o = FlashAttention(1, heads, S, S, D, causal=True)(q, k, v)
+        torch.cuda.synchronize()
+        assert torch.equal(o_all.local.view(1, heads, S, D), want_o), f"rank {rank}: gathered O differs"
+        o_all.barrier()
     finally:
         dist.destroy_process_group()
 
