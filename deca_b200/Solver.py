@@ -126,6 +126,14 @@ def solve_flash_attn(arch, B: int, H: int, S_q: int, S_kv: int, D: int, type_siz
         except AssertionError:
             continue
         results.append(cfg)
+        # the persistent form of the two-tile schedule (its O staging panels take 32 KB of the ring's space)
+        if cfg.q_tiles == 2 and cfg.Bc == 128 and cfg.p_tmem:
+            pers = FAConfig(**{**cfg.as_dict(), "persistent": True})
+            try:
+                check_config(pers, S_q, S_kv, D)
+            except AssertionError:
+                continue
+            results.append(pers)
     return results
 
 

@@ -29,6 +29,7 @@ class FAConfig:
     stages: int = 2  # K/V shared-memory ring depth (q_tiles = 2: slots of the ring K and V share)
     q_tiles: int = 1  # Q tiles a CTA works on alternately (1 or 2)
     p_tmem: bool = False  # keep P in tensor memory (MMA A operand) instead of shared memory
+    persistent: bool = False  # one CTA per SM walks the (head, Q-tile pair) items (q_tiles = 2, Bc = 128, p_tmem)
 
     @property
     def threads(self) -> int:
@@ -40,11 +41,13 @@ class FAConfig:
 
     def __str__(self):
         return (f"Br={self.Br},Bc={self.Bc},stages={self.stages},q_tiles={self.q_tiles}"
-                + (",p_tmem=1" if self.p_tmem else ""))
+                + (",p_tmem=1" if self.p_tmem else "") + (",persistent=1" if self.persistent else ""))
 
 
 def smem_bytes(cfg: FAConfig, D: int) -> int:
     q = cfg.q_tiles * cfg.Br * D * 2
+    if cfg.persistent:
+        return q + cfg.stages * cfg.Bc * D * 2 + 8 * 4096 + 2048  # ring + O staging panels
     if cfg.q_tiles == 2:
         kv = cfg.stages * cfg.Bc * D * 2  # one ring shared by K and V tiles
         p = 0 if cfg.p_tmem else 2 * cfg.Br * cfg.Bc * 2  # one P tile per Q tile
@@ -69,6 +72,8 @@ def check_config(cfg: FAConfig, S_q: int, S_kv: int, D: int) -> None:
     assert cfg.Br == 128
     assert cfg.Bc in (64, 128)
     assert cfg.q_tiles in (1, 2)
+    if cfg.persistent:
+        assert cfg.q_tiles == 2 and cfg.Bc == 128 and cfg.p_tmem
     if cfg.q_tiles == 2:
         # 64-key tiles: P must live in tensor memory and K_{j+2}, V_j, V_{j+1} are in flight together
         assert cfg.Bc == 128 or cfg.p_tmem
@@ -103,7 +108,7 @@ def build_flash_attn_to_file(shape, cfg: FAConfig, softmax_scale, arch: str, pat
 def native_cfg(cfg: FAConfig):
     from .. import native
 
-    return native.FaCfg(cfg.Br, cfg.Bc, cfg.stages, cfg.q_tiles, int(cfg.p_tmem))
+    return native.FaCfg(cfg.Br, cfg.Bc, cfg.stages, cfg.q_tiles, int(cfg.p_tmem), int(cfg.persistent))
 
 
 def bind(spec: KernelSpec):

@@ -45,7 +45,7 @@ class GemmCfg(ctypes.Structure):
 
 
 class FaCfg(ctypes.Structure):
-    _fields_ = [(n, ctypes.c_int) for n in ("Br", "Bc", "stages", "q_tiles", "p_tmem")]
+    _fields_ = [(n, ctypes.c_int) for n in ("Br", "Bc", "stages", "q_tiles", "p_tmem", "persistent")]
 
 
 def lib() -> ctypes.CDLL:

@@ -42,7 +42,8 @@ def run_native(native, q_bits, k_bits, v_bits, causal, scale=None, cfg=None):
         scale = 1.0 / float(np.sqrt(D))
     ccfg = None
     if cfg is not None:
-        ccfg = ctypes.byref(native.FaCfg(128, cfg.get("Bc", 128), cfg.get("stages", 2), cfg.get("q_tiles", 1), cfg.get("p_tmem", 0)))
+        ccfg = ctypes.byref(native.FaCfg(128, cfg.get("Bc", 128), cfg.get("stages", 2), cfg.get("q_tiles", 1), cfg.get("p_tmem", 0),
+                                         cfg.get("persistent", 0)))
     st = native.lib().deca_fa_fwd_f16(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), B, H, S_q, S_kv, D,
                                       ctypes.c_float(scale), int(causal), ccfg,
                                       ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
@@ -84,13 +85,17 @@ def test_cross_attention_lengths(native):
                                  dict(Bc=128, stages=2, q_tiles=2, p_tmem=1), dict(Bc=128, stages=5, q_tiles=2, p_tmem=1),
                                  dict(Bc=128, stages=3, p_tmem=1), dict(Bc=64, stages=2, p_tmem=1), dict(Bc=128, stages=1, p_tmem=1),
                                  dict(Bc=64, stages=4, q_tiles=2, p_tmem=1), dict(Bc=64, stages=8, q_tiles=2, p_tmem=1),
-                                 dict(Bc=64, stages=5, q_tiles=2, p_tmem=1)],
+                                 dict(Bc=64, stages=5, q_tiles=2, p_tmem=1),
+                                 dict(Bc=128, stages=4, q_tiles=2, p_tmem=1, persistent=1),
+                                 dict(Bc=128, stages=2, q_tiles=2, p_tmem=1, persistent=1),
+                                 dict(Bc=128, stages=3, q_tiles=2, p_tmem=1, persistent=1)],
                          ids=lambda c: ",".join(f"{k}={v}" for k, v in c.items()))
 def test_configs_match_oracle(native, cfg):
     for D in (64, 128):
         S = 768 if cfg.get("q_tiles", 1) == 2 else 640
         if native.lib().deca_fa_fwd_f16_check_config(1, 2, S, S, D, 1, ctypes.byref(
-                native.FaCfg(128, cfg["Bc"], cfg["stages"], cfg.get("q_tiles", 1), cfg.get("p_tmem", 0)))) != 0:
+                native.FaCfg(128, cfg["Bc"], cfg["stages"], cfg.get("q_tiles", 1), cfg.get("p_tmem", 0),
+                             cfg.get("persistent", 0)))) != 0:
             continue
         q, k, v = make_qkv(1, 2, S, S, D, seed=5)
         for causal in (False, True):
@@ -160,3 +165,35 @@ def test_argument_errors(native):
     bad = native.FaCfg(128, 128, 4, 1, 0)  # 4 stages of 64 KB do not fit at D = 128
     assert L.deca_fa_fwd_f16(p, p, p, p, 1, 1, 128, 128, 128, f, 0, ctypes.byref(bad), st) == -4
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("shape", [(1, 150, 256, 64), (2, 3, 1024, 128), (5, 31, 512, 128), (1, 2, 2560, 64)],
+                         ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("causal", [False, True], ids=["full", "causal"])
+def test_persistent_kernel_matches_one_item_per_cta(native, shape, causal):
+    """The persistent schedule does the arithmetic of the two-tile kernel item by item: identical
+    bits, whatever the number of items per CTA (fewer items than SMs, several items per CTA, an odd
+    number of Q-tile pairs per head); one head is also checked against the oracle."""
+    B, H, S, D = shape
+    q, k, v = make_qkv(B, H, S, S, D, seed=9)
+    cfg = dict(Bc=128, stages=4 if D == 64 or S >= 512 else 2, q_tiles=2, p_tmem=1)
+    plain = run_native(native, q, k, v, causal, cfg=cfg)
+    pers = run_native(native, q, k, v, causal, cfg=dict(cfg, persistent=1))
+    assert np.array_equal(plain, pers)
+    check(q[:1, :1], k[:1, :1], v[:1, :1], pers[:1, :1], causal)
+
+
+def test_persistent_config_rules(native):
+    L = native.lib()
+
+    def rc(*fields, S=1024, D=128):
+        return L.deca_fa_fwd_f16_check_config(1, 2, S, S, D, 0, ctypes.byref(native.FaCfg(*fields)))
+
+    assert rc(128, 128, 4, 2, 1, 1) == 0
+    assert rc(128, 128, 4, 1, 1, 1) == -4  # two Q tiles only
+    assert rc(128, 64, 4, 2, 1, 1) == -4   # 128-key tiles only
+    assert rc(128, 128, 4, 2, 0, 1) == -4  # P in tensor memory only
+    assert rc(128, 128, 5, 2, 1, 1) == -4  # five slots and the staging panels do not fit at D = 128
+    assert rc(128, 128, 8, 2, 1, 1, D=64) == 0
+    assert rc(128, 128, 4, 2, 1, 2) == -4
+    assert rc(128, 128, 4, 2, 1, 1, S=384) == -4  # S_q % 256
