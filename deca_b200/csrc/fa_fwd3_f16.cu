@@ -18,6 +18,10 @@
 // All mbarrier waits are bounded (ptx.cuh); a wait that runs out raises the CTA's abort flag and
 // every role falls through to the common teardown.
 #include <atomic>
+#include <map>
+#include <mutex>
+#include <tuple>
+#include <vector>
 
 #include "fa_softmax.cuh"
 #include "ptx.cuh"
@@ -37,9 +41,9 @@ struct Fa3Args {
     int stages;  // K/V ring slots
     float sl2;
     int n_peers;
-    int n_pairs;  // Q-tile pairs per head
-    int n_items;  // heads x pairs
-    int group;    // items a CTA takes in a row: 2 when causal (a long pair and its short mirror), else 1
+    int n_pairs;    // Q-tile pairs per head
+    int n_heads;    // B * H
+    int sec_heads;  // causal: heads per section (their K and V together fit in half of L2)
     DeviceStatus *status;
 };
 
@@ -87,26 +91,49 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    // item -> (Q-tile pair, head); tiles visited by group A / B of that pair.  Causal items come in
-    // groups of two of one head, pair n_pairs - 1 - x and then pair x: every group costs the same,
-    // so handing the groups out round-robin balances the CTAs.
-    auto decode = [&](int item, int &pair, int &bh, int &n_a, int &n_b) {
-        bh = item / g.n_pairs;
-        const int y = item - bh * g.n_pairs;
-        if (g.group == 2)
-            pair = (y & 1) ? (y >> 1) : (g.n_pairs - 1 - (y >> 1));
-        else
-            pair = g.causal ? (g.n_pairs - 1 - y) : y;
+    // The CTA's items, in the order every role walks them.
+    // Non-causal (all items cost the same): items c, c + grid, ... of the head-major list, so the
+    // CTAs that run together share a few heads' K and V.
+    // Causal (pair p costs 2p + 2 tiles): the heads are cut into sections whose K and V fit in half of
+    // L2; within a section the items are sorted longest first (pair n-1 of every head, then pair n-2,
+    // ...) and dealt out in rounds of `grid` that alternate direction (CTA c takes position c of an
+    // even round and grid - 1 - c of an odd one), which evens out the CTAs' totals.
+    struct ItemWalk {
+        int sec, round;
+    };
+    // advances to the CTA's next item (the first one when `first`); false when it has none left
+    auto item_next = [&](ItemWalk &w, int &pair, int &bh, bool first) {
+        const int G = (int)gridDim.x, c = (int)blockIdx.x;
+        if (!first) ++w.round;
+        if (!g.causal) {
+            const int item = w.round * G + c;
+            if (item >= g.n_heads * g.n_pairs) return false;
+            bh = item / g.n_pairs;
+            pair = item - bh * g.n_pairs;
+            return true;
+        }
+        while (true) {
+            const int h0 = w.sec * g.sec_heads;
+            if (h0 >= g.n_heads) return false;
+            const int heads = min(g.sec_heads, g.n_heads - h0);
+            const int n = heads * g.n_pairs;  // positions of the section, longest pairs first
+            if (w.round * G >= n) {
+                ++w.sec;
+                w.round = 0;
+                continue;
+            }
+            const int pos = w.round * G + ((w.round & 1) ? (G - 1 - c) : c);
+            if (pos < n) {
+                pair = g.n_pairs - 1 - pos / heads;
+                bh = h0 + pos % heads;
+                return true;
+            }
+            ++w.round;  // the section's last, partial round has no position for this CTA
+        }
+    };
+    auto tiles_of = [&](int pair, int &n_a, int &n_b) {
         n_a = g.causal ? ((2 * pair + 1) * kBr + kBc - 1) / kBc : g.S_kv / kBc;
         n_b = g.causal ? ((2 * pair + 2) * kBr + kBc - 1) / kBc : g.S_kv / kBc;
-    };
-    // this CTA's items: groups blockIdx.x, blockIdx.x + grid, ...; every role walks its own copy
-    struct ItemWalk {
-        int step, sub;
-    };
-    auto item_of = [&](const ItemWalk &w) { return w.step * g.group + w.sub < g.n_items ? w.step * g.group + w.sub : -1; };
-    auto item_next = [&](ItemWalk &w) {
-        if (++w.sub == g.group) w.sub = 0, w.step += (int)gridDim.x;
     };
 
     if (threadIdx.x == 0) {
@@ -151,15 +178,16 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             bool ok = true;
             RingPos rp{0, 0u};
             int n_local = 0;
-            ItemWalk walk{(int)blockIdx.x, 0};
-            for (int item = item_of(walk); item >= 0 && ok; item_next(walk), item = item_of(walk), ++n_local) {
-                int pair, bh, n_a, n_b;
-                decode(item, pair, bh, n_a, n_b);
+            ItemWalk walk{0, 0};
+            int pair, bh;
+            for (bool more = item_next(walk, pair, bh, true); more && ok; more = item_next(walk, pair, bh, false), ++n_local) {
+                int n_a, n_b;
+                tiles_of(pair, n_a, n_b);
                 const int q_row0 = bh * g.S_q + pair * 2 * kBr;
                 const int kv_row0 = bh * g.S_kv;
                 // the Q tiles are free once every score MMA of the previous item has completed
                 if (n_local > 0 && !mbar_wait(q_free, (uint32_t)((n_local - 1) & 1), abort_flag)) {
-                    report_detail(g.status, 0, 1, item);
+                    report_detail(g.status, 0, 1, n_local);
                     ok = false;
                     break;
                 }
@@ -223,14 +251,15 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             RingPos kp{0, 0u}, vp{1 % stages, (uint32_t)((1 / stages) & 1)};
             uint32_t cnt[2] = {0u, 0u};
             int n_local = 0;
-            ItemWalk walk{(int)blockIdx.x, 0};
-            for (int item = item_of(walk); item >= 0 && ok; item_next(walk), item = item_of(walk), ++n_local) {
-                int pair, bh, n_a, n_b;
-                decode(item, pair, bh, n_a, n_b);
+            ItemWalk walk{0, 0};
+            int pair, bh;
+            for (bool more = item_next(walk, pair, bh, true); more && ok; more = item_next(walk, pair, bh, false), ++n_local) {
+                int n_a, n_b;
+                tiles_of(pair, n_a, n_b);
                 // first tile: Q and K_0
                 if (!mbar_wait(q_full, (uint32_t)(n_local & 1), abort_flag) ||
                     !mbar_wait(kv_full(kp.slot), kp.par, abort_flag)) {
-                    report_detail(g.status, 1, 3, item);
+                    report_detail(g.status, 1, 3, n_local);
                     ok = false;
                     break;
                 }
@@ -306,10 +335,11 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag)) != 0;
         };
 
-        ItemWalk walk{(int)blockIdx.x, 0};
-        for (int item = item_of(walk); item >= 0 && ok; item_next(walk), item = item_of(walk)) {
-            int pair, bh, n_a, n_b;
-            decode(item, pair, bh, n_a, n_b);
+        ItemWalk walk{0, 0};
+        int pair, bh;
+        for (bool more = item_next(walk, pair, bh, true); more && ok; more = item_next(walk, pair, bh, false)) {
+            int n_a, n_b;
+            tiles_of(pair, n_a, n_b);
             const int qt = 2 * pair + grp;
             const int row_abs = qt * kBr + r;
             const int n_kv = grp == 0 ? n_a : n_b;
@@ -418,6 +448,66 @@ int launch_fa3(const CUtensorMap &tmQ, const CUtensorMap &tmK, const CUtensorMap
 
 }  // namespace
 
+namespace {
+
+// Causal schedules deal the items of one section of heads (longest pairs first) to the CTAs in
+// rounds of alternating direction, exactly as the kernel's item walk does; this is the largest
+// CTA total that results, in tiles.
+double causal_balance(int grid, int n_heads, int n_pairs, int sec_heads) {
+    std::vector<long long> load(grid, 0);
+    long long total = 0;
+    for (int h0 = 0; h0 < n_heads; h0 += sec_heads) {
+        const int heads = sec_heads < n_heads - h0 ? sec_heads : n_heads - h0;
+        const int n = heads * n_pairs;
+        for (int pos = 0; pos < n; ++pos) {
+            const int r = pos / grid, k = pos % grid;
+            const int cost = 2 * (n_pairs - 1 - pos / heads) + 2;
+            load[(r & 1) ? grid - 1 - k : k] += cost;
+            total += cost;
+        }
+    }
+    long long mx = 1;
+    for (long long v : load) mx = v > mx ? v : mx;
+    return (double)total / grid / (double)mx;
+}
+
+// Heads per section for a causal problem: the candidate with the best product of the balance of
+// its static schedule and an L2 term (measured on B200: the K and V of a section cost nothing up
+// to a quarter of L2, about 14 % at a full L2, more beyond).  Cached per problem.
+int choose_sec_heads(int grid, int n_heads, int n_pairs, long long kv_bytes_per_head, long long l2_bytes) {
+    static std::mutex mu;
+    static std::map<std::tuple<int, int, int, long long, long long>, int> cache;
+    const auto key = std::make_tuple(grid, n_heads, n_pairs, kv_bytes_per_head, l2_bytes);
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    int best = n_heads;
+    double best_score = -1.0;
+    for (int h = 1; h <= n_heads; h = (h < 64 ? h + 1 : (h < 256 ? h + 8 : h * 2))) {
+        const int hh = h > n_heads ? n_heads : h;
+        if ((long long)n_heads * n_pairs * (n_heads / hh + 1) > 50000000ll) continue;  // keep the search cheap
+        const double frac = (double)hh * (double)kv_bytes_per_head / (double)l2_bytes;
+        double f = 1.0;
+        if (frac > 0.25) f -= 0.14 * ((frac < 1.0 ? frac : 1.0) - 0.25) / 0.75;
+        if (frac > 1.0) f -= 0.05 * ((frac < 4.0 ? frac : 4.0) - 1.0);
+        const double score = causal_balance(grid, n_heads, n_pairs, hh) * f;
+        if (score > best_score + 1e-9) best_score = score, best = hh;
+    }
+    {
+        // the whole problem as one section is always a candidate
+        const double frac = (double)n_heads * (double)kv_bytes_per_head / (double)l2_bytes;
+        double f = 1.0;
+        if (frac > 0.25) f -= 0.14 * ((frac < 1.0 ? frac : 1.0) - 0.25) / 0.75;
+        if (frac > 1.0) f -= 0.05 * ((frac < 4.0 ? frac : 4.0) - 1.0);
+        if ((long long)n_heads * n_pairs <= 50000000ll && causal_balance(grid, n_heads, n_pairs, n_heads) * f > best_score + 1e-9)
+            best = n_heads;
+    }
+    cache[key] = best;
+    return best;
+}
+
+}  // namespace
+
 size_t fa3_smem_bytes(int D, int stages) {
     return 1024 + 2 * (size_t)kBr * D * 2 + (size_t)stages * kBc * D * 2 + kOStageBytes + 8 * (2 * (size_t)stages + 16);
 }
@@ -443,17 +533,19 @@ int fa3_launch(const CUtensorMap &tmQ, const CUtensorMap &tmK, const CUtensorMap
     g.n_pairs = S_q / (2 * kBr);
     const int64_t items = (int64_t)g.n_pairs * B * H;
     if (items > 2147483647ll) return DECA_ERR_SHAPE;
-    g.n_items = (int)items;
-    g.group = (causal && g.n_pairs % 2 == 0) ? 2 : 1;
+    g.n_heads = B * H;
     g.status = device_status_ptr();
     if (!g.status) return (int)cudaErrorUnknown;
-    int dev = 0, sms = 0;
+    int dev = 0, sms = 0, l2 = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return (int)e;
-    const int64_t steps = (items + g.group - 1) / g.group;
-    const unsigned grid = (unsigned)(steps < sms ? steps : sms);
+    e = cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev);
+    if (e != cudaSuccess) return (int)e;
+    const unsigned grid = (unsigned)(items < sms ? items : sms);
+    g.sec_heads = g.n_heads;
+    if (causal) g.sec_heads = choose_sec_heads((int)grid, g.n_heads, g.n_pairs, 2ll * S_kv * D * 2, l2);
     const size_t smem = fa3_smem_bytes(D, c.stages);
     return D == 128 ? launch_fa3<128>(tmQ, tmK, tmV, tmO, peers, g, grid, smem, st)
                     : launch_fa3<64>(tmQ, tmK, tmV, tmO, peers, g, grid, smem, st);
