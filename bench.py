@@ -47,9 +47,9 @@ NCU_TRAFFIC_BYTES = {
     "rowwise_softmax_f16_16384x4096": 217628672,
     # profiles/gemm_f16_4096.md: 80.51 MB read + 6.59 MB written (C mostly still in L2)
     "gemm_f16_4096x4096x4096": 87099392,
-    # profiles/fa_fwd2_f16_1x16x4096x128.md captured B = 1 (50.40 MB + 2.24 MB); traffic grows
+    # profiles/fa_fwd3_f16_1x16x4096x128.md captured B = 1 (50.42 MB + 1.17 MB); traffic grows
     # in proportion to the batch: x 4 for B = 4
-    "fa_fwd_f16_4x16x4096x128": 210591744,
+    "fa_fwd_f16_4x16x4096x128": 206323712,
 }
 
 
