@@ -30,14 +30,12 @@ def solve_gemm_tc(arch, M: int, N: int, K: int, type_size: int = 2, count: int =
                   acc_splits: int = 1):
     """Enumerates 16-bit tensor-core GEMM tile configurations (see ``GemmConfig``).
 
-    arch supplies ``max_dyn_smem_per_block``, ``tmem_columns`` and ``sm_nums``.  ``acc_f16`` is
-    accepted for call-site compatibility; the tcgen05 kernel accumulates in fp32 only, so asking
-    for fp16 accumulation yields no config.
+    arch supplies ``max_dyn_smem_per_block``, ``tmem_columns`` and ``sm_nums``.  ``acc_f16`` and
+    ``acc_splits`` are accepted for call-site compatibility and change nothing: the tcgen05 kernel
+    always accumulates in fp32, which also serves an operator built with ``acc="fp16"``.
     """
     from .kernels.gemm_b200 import SMEM_RESERVED, GemmConfig, check_config, stream_k_plan
 
-    if acc_f16:
-        return []
     s = Solver()
     bm, bn, st, epi, acc = BitVecs("bm bn st epi acc", 32)
     k_ = BitVecVal(K, 32)
