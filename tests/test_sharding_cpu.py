@@ -88,3 +88,32 @@ def test_two_rank_gloo_sharding_matches_unsharded():
         assert p.exitcode == 0
     assert sorted(r[0] for r in results) == [0, 1]
     assert all(r[1] and r[2] and r[3] for r in results), results
+
+
+def test_gathered_output_host_checks():
+    """GatheredOutput and the gather wrappers validate their arguments on the host before any
+    launch (CPU tensors suffice: nothing is launched)."""
+    import pytest
+    import torch
+
+    from deca_b200.sharding import GatheredOutput, attention_gather, gemm_gather
+
+    copies = [torch.zeros(8, 16, dtype=torch.float16) for _ in range(2)]
+    out = GatheredOutput.from_tensors(copies, 1)
+    assert (out.world, out.rank, out.rows_per_rank) == (2, 1, 4)
+    assert out.ptrs == [t.data_ptr() for t in copies] and out.local is copies[1]
+    with pytest.raises(ValueError):
+        GatheredOutput.from_tensors([torch.zeros(9, 16), torch.zeros(9, 16)], 0)  # 9 rows over 2 ranks
+    with pytest.raises(ValueError):
+        GatheredOutput.from_tensors([torch.zeros(8, 16), torch.zeros(8, 8)], 0)  # shapes differ
+    with pytest.raises(ValueError):
+        GatheredOutput(copies[0], [copies[1].data_ptr(), copies[0].data_ptr()], 0, 4)  # ptrs[rank] is not local
+    a = torch.zeros(5, 32, dtype=torch.float16)  # 5 rows, but a rank's share is 4
+    b = torch.zeros(32, 16, dtype=torch.float16)
+    with pytest.raises(ValueError):
+        gemm_gather(a, b, out)
+    with pytest.raises(ValueError):
+        gemm_gather(a[:4], torch.zeros(32, 8, dtype=torch.float16), out)  # N does not match the gathered buffer
+    q = torch.zeros(1, 1, 4, 8, dtype=torch.float16)  # 4 rows of 8: the buffer holds 16 columns
+    with pytest.raises(ValueError):
+        attention_gather(q, q, q, out)
