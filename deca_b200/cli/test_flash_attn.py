@@ -8,6 +8,7 @@ Flags, progress lines and the final record follow the reference's test_flash_att
 """
 
 import argparse
+import csv
 import os
 
 
@@ -108,6 +109,17 @@ def main(argv=None):
         print(f"{'B':>3} {'H':>3} {'S':>6} {'D':>4} | {'DeCA':>8} {'SDPA':>8} {'ratio':>6} | config")
         for (B, H, S_q, _, D), cfg, tflops, sdpa in summary:
             print(f"{B:>3} {H:>3} {S_q:>6} {D:>4} | {tflops:>8.2f} {sdpa:>8.2f} {tflops / sdpa:>6.3f} | {cfg}")
+    if args.sweep:
+        # the sweep's table as a file, next to the log (the GEMM CLI's CSV, for this operator)
+        name = "flash_attn_causal_sweep.csv" if args.causal else "flash_attn_sweep.csv"
+        csv_path = os.path.join(os.path.dirname(_tune.log_path()), name)
+        with open(csv_path, "w", newline="") as f:
+            w = csv.writer(f)
+            w.writerow(["B", "H", "S_q", "S_kv", "D", "causal", "DeCA_TFLOPS", "SDPA_TFLOPS", "ratio", "config"])
+            for (B, H, S_q, S_kv, D), cfg, tflops, sdpa in summary:
+                w.writerow([B, H, S_q, S_kv, D, int(args.causal), f"{tflops:.4f}", f"{sdpa:.4f}",
+                            f"{tflops / sdpa if sdpa else float('nan'):.4f}", str(cfg)])
+        print(f"wrote {len(summary)} shapes to {csv_path}", flush=True)
 
 
 if __name__ == "__main__":

@@ -8,6 +8,7 @@ Flags, progress lines and the final record follow the reference's test_rowwise.p
 """
 
 import argparse
+import csv
 import os
 
 
@@ -108,6 +109,16 @@ def main(argv=None):
         for (M, N), cfg, gbps, torch_gbps in summary:
             print(f"{M:>6} {N:>7} | {gbps:>7.0f} {torch_gbps:>7.0f} "
                   f"{100 * gbps / arch.dram_bw:>5.0f} {gbps / torch_gbps:>6.3f} | {cfg}")
+    if args.sweep:
+        # the sweep's table as a file, next to the log (the GEMM CLI's CSV, for this operator)
+        csv_path = os.path.join(os.path.dirname(_tune.log_path()), f"{args.op}_{args.dtype}_sweep.csv")
+        with open(csv_path, "w", newline="") as f:
+            w = csv.writer(f)
+            w.writerow(["M", "N", "DeCA_GBps", "torch_GBps", "ratio", "config"])
+            for (M, N), cfg, gbps, torch_gbps in summary:
+                w.writerow([M, N, f"{gbps:.2f}", f"{torch_gbps:.2f}",
+                            f"{gbps / torch_gbps if torch_gbps else float('nan'):.4f}", str(cfg)])
+        print(f"wrote {len(summary)} shapes to {csv_path}", flush=True)
 
 
 if __name__ == "__main__":
