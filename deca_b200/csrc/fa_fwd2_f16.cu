@@ -469,7 +469,12 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     for (int blk = 0; blk < D / 64; ++blk)
                         tma_store_2d(&peers.m[pr], stage0 + blk * 16384 + q * 4096, blk * 64, q_row0 + grp * kBr + q * 32);
                 tma_store_commit();
-                tma_store_wait<0>();
+                // the CTA may leave once its stores have read shared memory (the writes complete with
+                // the grid); stores to peers are waited for in full
+                if (g.n_peers > 0)
+                    tma_store_wait<0>();
+                else
+                    tma_store_wait_read<0>();
             }
         }
         __syncwarp();

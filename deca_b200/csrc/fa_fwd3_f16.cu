@@ -420,7 +420,14 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             *abort_flag = 1;
             report_timeout(g.status, 0x413u);
         }
-        if (lane == 0) tma_store_wait<0>();
+        // the CTA may leave once its stores have read shared memory (the writes complete with the
+        // grid); stores to peers are waited for in full
+        if (lane == 0) {
+            if (g.n_peers > 0)
+                tma_store_wait<0>();
+            else
+                tma_store_wait_read<0>();
+        }
         __syncwarp();
     }
 

@@ -263,7 +263,7 @@ gemm16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             }
             aph ^= 1u;
         }
-        if (lane == 0) tma_store_wait<0>();
+        if (lane == 0) tma_store_wait_read<0>();  // the writes complete with the grid
         __syncwarp();
     }
 

@@ -99,12 +99,18 @@ def default_config(M: int, N: int, K: int) -> GemmConfig:
 
     if tiles(256, 256) >= sms:
         bm, bn, stages, acc = 256, 256, 3, 1
-    elif N > 128:
-        bm, bn, stages, acc = 128, 256, 4, 2
     else:
-        bm, bn, stages, acc = 128, 128, 6, 2
-    if N <= 64:
-        bm, bn, stages, acc = 128, 64, 8, 2
+        # fewer tiles than SMs: weigh the share of SMs a tile shape keeps busy against the rate of
+        # its main loop (narrower tiles re-read A from shared memory more often per flop)
+        cands = [((128, 256, 4, 2), 1.0), ((128, 128, 6, 2), 0.8), ((128, 64, 8, 2), 0.55)]
+        def score(c):
+            (bm_, bn_, _, _), rate = c
+            if bn_ > max(64, 2 * N):
+                return 0.0
+            t = tiles(bm_, bn_)
+            useful = M * N / (t * bm_ * bn_)  # partial tiles compute zero-filled rows / columns
+            return rate * useful * t / (-(-t // sms) * sms)
+        (bm, bn, stages, acc), _ = max(cands, key=score)
     stages = max(2, min(stages, -(-K // 64)))  # no deeper than the number of K blocks
     gm = -(-M // bm)
     raster = 8
