@@ -77,14 +77,15 @@ def solve_gemm_tc(arch, M: int, N: int, K: int, type_size: int = 2, count: int =
                 sk = GemmConfig(**{**cfg.as_dict(), "stream_k": True})
                 if stream_k_plan(sk, M, N, K, sms) is not None:
                     results.append(sk)
-    # CTA pairs (tcgen05 cta_group::2) on a 512 x 256 tile: worth offering once the problem has a
-    # pair tile for half of the SMs
-    if -(-M // 512) * -(-N // 256) >= arch.sm_nums // 4:
-        for st in (3, 4):
+    # CTA pairs (tcgen05 cta_group::2): (2 BM) x BN tiles whose CTAs fetch half of the B columns each
+    for bm_, bn_, acc_ in ((256, 256, 1), (128, 256, 2), (128, 256, 1), (256, 128, 2), (128, 128, 2)):
+        if -(-M // (2 * bm_)) * -(-N // bn_) < 8 or bn_ > max(2 * N - 1, 128):
+            continue
+        for st in (3, 4, 6, 8):
             for ras in (1, 2, 4, 8, 16):
-                if ras > 1 and ras > -(-M // 512):
+                if ras > 1 and ras > -(-M // (2 * bm_)):
                     continue
-                cfg = GemmConfig(BM=256, BN=256, BK=64, stages=st, raster=ras, epi_smem=True, cta_group=2, acc_bufs=1)
+                cfg = GemmConfig(BM=bm_, BN=bn_, BK=64, stages=st, raster=ras, epi_smem=True, cta_group=2, acc_bufs=acc_)
                 try:
                     check_config(cfg, M, N, K)
                 except AssertionError:

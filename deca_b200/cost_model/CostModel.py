@@ -104,7 +104,13 @@ def gemm_tc_score(cfg, arch: Arch, M: int, N: int, K: int) -> float:
     if cfg.acc_bufs == 2 and not cfg.epi_smem:
         epi = 0.97
 
-    return wave_eff * useful * pipe * epi / (t_flop / t_mma)
+    rate = 1.0
+    if pair:
+        # measured: the pair kernel matches the one-CTA kernel tile for tile (512 x 256 pair tile
+        # 1312-1371 TFLOPS at 4096^3, 256 x 256 pair tile 1163, narrower ones 700-850), so its
+        # smaller tiles are ranked like the one-CTA tiles with the same rows and columns per CTA
+        rate = {(256, 256): 0.97, (128, 256): 0.85, (256, 128): 0.62, (128, 128): 0.52}.get((cfg.BM, cfg.BN), 0.5)
+    return rate * wave_eff * useful * pipe * epi / (t_flop / t_mma)
 
 
 def rank_gemm_configs(configs, arch: Arch, M: int, N: int, K: int, top_n: int | None = None):

@@ -7,8 +7,8 @@
 
 namespace deca {
 
-// Host-only validity of a cta_group == 2 config (BM = 256 rows per CTA, BN = 256, one accumulator,
-// staged epilogue, 2-4 stages).
+// Host-only validity of a cta_group == 2 config (BM = 128 or 256 rows per CTA, BN = 128 or 256,
+// accumulators within 512 tensor-memory columns, staged epilogue, no stream-K).
 int gemm16_pair_check(int64_t M, int64_t N, int64_t K, const deca_gemm_cfg *cfg);
 
 // Launches the pair kernel; shapes, alignment and the config have been checked by the caller.

@@ -2,12 +2,15 @@
 // fp32 accumulation in tensor memory.  Same operation and reference counterpart as gemm_f16.cu
 // (the mma.sync kernel of src/kernels/gemm_tir.py:123-386); this is the form for large problems.
 //
-// A cluster of two CTAs owns a 512 x 256 output tile.  Each CTA holds 256 rows of A and of the
-// accumulator (two 128-row halves, all 512 tensor-memory columns) and 128 of the 256 columns of
-// B per 64-deep k block; one thread of the even CTA issues MMAs of M = 256 (128 rows from each
-// CTA) x N = 256, and the hardware reads the other CTA's operands from that CTA's shared memory.
-// Against the one-CTA 256 x 256 tile this moves 48 KB instead of 64 KB per k block into each
-// SM and reads 8 KB instead of 12 KB of shared memory per MMA, which is what bounds that kernel.
+// A cluster of two CTAs owns a (2 BM) x BN output tile, BM = 128 or 256 rows per CTA, BN = 128 or
+// 256.  Each CTA holds its BM rows of A and of the accumulator (BM / 128 halves of BN tensor-memory
+// columns per accumulator buffer) and BN / 2 of the B columns per 64-deep k block; one thread of
+// the even CTA issues MMAs of M = 256 (128 rows from each CTA) x N = BN, and the hardware reads
+// the other CTA's operands from that CTA's shared memory.  Against the one-CTA kernel with the
+// same rows and columns per CTA this moves a B half less per k block into each SM and reads half
+// of B from shared memory per MMA (BM = 256, BN = 256: 48 KB instead of 64 KB and 8 KB instead
+// of 12 KB; BM = 128, BN = 256: 32 KB instead of 48 KB and 8 KB instead of 12 KB), which is what
+// bounds the narrow one-CTA tiles of small problems.
 //   warp 0      TMA producer in both CTAs: own A rows and own B columns into the own ring; the
 //               bytes are credited to the even CTA's slot barrier (no multicast).
 //   warp 1      tensor-memory allocation (both CTAs); MMA issuer (even CTA): tcgen05.commit
@@ -27,14 +30,8 @@
 namespace deca {
 namespace {
 
-constexpr int kCtaRows = 256;  // rows of the tile held by one CTA
-constexpr int kPairRows = 2 * kCtaRows;
-constexpr int kTileN = 256;
 constexpr int kBK = 64;
 constexpr int kThreads = 192;
-constexpr uint32_t kAStageBytes = kCtaRows * kBK * 2;       // 32 KB
-constexpr uint32_t kBStageBytes = (kTileN / 2) * kBK * 2;   // 16 KB: this CTA's 128 columns
-constexpr uint32_t kStageBytes = kAStageBytes + kBStageBytes;
 constexpr uint32_t kEpiBytes = 4 * 2 * 4096;
 constexpr uint32_t kTmemCols = 512;
 
@@ -44,6 +41,7 @@ struct PairArgs {
     int gm, gn;  // pair tiles along M and N
     int raster;
     int stages;
+    int acc_bufs;
     DeviceStatus *status;
 };
 
@@ -57,11 +55,19 @@ __device__ __forceinline__ void pair_tile_coords(int tile, const PairArgs &g, in
     n_tile = local / rows;
 }
 
-template <int DT>
+// HALVES = BM / 128 MMA row halves per CTA, TN = BN.
+template <int DT, int HALVES, int TN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    const __grid_constant__ CUtensorMap tmC, const PairArgs g) {
     using P = Pack16<DT>;
+    constexpr int kCtaRows = HALVES * 128;  // rows of the tile held by one CTA
+    constexpr int kPairRows = 2 * kCtaRows;
+    constexpr int kTileN = TN;
+    constexpr uint32_t kAStageBytes = kCtaRows * kBK * 2;
+    constexpr uint32_t kBStageBytes = (kTileN / 2) * kBK * 2;  // this CTA's half of the columns
+    constexpr uint32_t kStageBytes = kAStageBytes + kBStageBytes;
+    constexpr uint32_t kAccCols = HALVES * kTileN;  // tensor-memory columns of one accumulator buffer
     constexpr uint32_t kIdesc = make_idesc_f16(DT, false, true, 256, kTileN);
 
     extern __shared__ uint8_t smem_raw[];
@@ -76,10 +82,10 @@ gemm16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const uint32_t sBar = sEpi + kEpiBytes;
     auto full = [&](int i) { return sBar + 8u * i; };
     auto empty = [&](int i) { return sBar + 8u * (stages + i); };
-    const uint32_t tfull = sBar + 8u * (2 * stages);
-    const uint32_t tempty = sBar + 8u * (2 * stages + 1);
-    const uint32_t drain_bar = sBar + 8u * (2 * stages + 2);
-    const uint32_t slot_addr = sBar + 8u * (2 * stages + 3);
+    auto tfull = [&](int i) { return sBar + 8u * (2 * stages + i); };
+    auto tempty = [&](int i) { return sBar + 8u * (2 * stages + 2 + i); };
+    const uint32_t drain_bar = sBar + 8u * (2 * stages + 4);
+    const uint32_t slot_addr = sBar + 8u * (2 * stages + 5);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + (slot_addr - base));
     volatile uint32_t *abort_flag = tmem_slot + 1;
 
@@ -96,8 +102,10 @@ gemm16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             mbar_init(full(i), 1);
             mbar_init(empty(i), 1);
         }
-        mbar_init(tfull, 1);
-        mbar_init(tempty, 8);  // four epilogue warps of each CTA
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(tfull(i), 1);
+            mbar_init(tempty(i), 8);  // four epilogue warps of each CTA
+        }
         mbar_init(drain_bar, 1);
         fence_barrier_init();
         prefetch_tensormap(&tmA);
@@ -153,15 +161,16 @@ gemm16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (even CTA)
         if (lane == 0 && rank == 0) {
-            int s = 0;
+            int s = 0, a = 0;
             uint32_t ph = 0, aph = 0;
             bool ok = true;
             for (int tile = pair_id; tile < total_tiles && ok; tile += n_pairs) {
-                if (!mbar_wait(tempty, aph ^ 1u, abort_flag)) {
+                if (!mbar_wait(tempty(a), aph ^ 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + (uint32_t)a * kAccCols;
                 for (int kb = 0; kb < g.num_kb; ++kb) {
                     if (!mbar_wait(full(s), ph, abort_flag)) {
                         ok = false;
@@ -176,17 +185,17 @@ gemm16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                         // 64-column blocks kBK*128 B apart, 16 k = 2048 B
                         const uint64_t bdesc = make_smem_desc(b_addr, kBK * 128, 1024) + k * (2048 >> 4);
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
+                        for (int h = 0; h < HALVES; ++h) {
                             const uint64_t adesc = make_smem_desc(a_addr, 16, 1024) + ((h * (128 * 128) + k * 32) >> 4);
-                            umma_f16_ss_pair(tmem_base + h * kTileN, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                            umma_f16_ss_pair(d_tmem + h * kTileN, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
                         }
                     }
                     umma_commit_pair(empty(s), 3);  // frees the slot in both CTAs
                     if (++s == stages) s = 0, ph ^= 1u;
                 }
                 if (!ok) break;
-                umma_commit_pair(tfull, 3);
-                aph ^= 1u;
+                umma_commit_pair(tfull(a), 3);
+                if (++a == g.acc_bufs) a = 0, aph ^= 1u;
             }
             if (!ok) {
                 if (*abort_flag == 0) {
@@ -203,15 +212,16 @@ gemm16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     } else {
         // ------------------------------------------------------------------ epilogue (both CTAs)
         const int q = warp & 3;
+        int a = 0;
         uint32_t aph = 0;
         uint32_t panel = 0;
         const uint32_t my_epi = sEpi + q * 8192;
-        const uint32_t pair_tempty = cluster_map(tempty, 0);
+        const uint32_t pair_tempty[2] = {cluster_map(tempty(0), 0), cluster_map(tempty(1), 0)};
         for (int tile = pair_id; tile < total_tiles; tile += n_pairs) {
             int mt, nt;
             pair_tile_coords(tile, g, mt, nt);
             const int m0 = mt * kPairRows + (int)rank * kCtaRows, n0 = nt * kTileN;
-            const bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull, aph, abort_flag));
+            const bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(tfull(a), aph, abort_flag));
             if (!ok) {
                 if (lane == 0 && *abort_flag == 0) {
                     *abort_flag = 1;
@@ -220,19 +230,19 @@ gemm16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16);
+            const uint32_t t_acc = tmem_base + (uint32_t)a * kAccCols + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-            for (int jj = 0; jj < 2 * (kTileN / 64); ++jj) {
+            for (int jj = 0; jj < HALVES * (kTileN / 64); ++jj) {
                 const int h = jj / (kTileN / 64), j = jj % (kTileN / 64);
                 uint32_t r0[32], r1[32];
                 tmem_ld_32x32b_x32(t_acc + h * kTileN + j * 64, r0);
                 tmem_ld_32x32b_x32(t_acc + h * kTileN + j * 64 + 32, r1);
                 tmem_ld_wait();
-                if (jj == 2 * (kTileN / 64) - 1) {
+                if (jj == HALVES * (kTileN / 64) - 1) {
                     // this CTA's half of the accumulator is in registers: tell the issuing CTA
                     tc_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(pair_tempty);
+                    if (lane == 0) mbar_arrive_cluster(pair_tempty[a]);
                 }
                 uint32_t p[32];
 #pragma unroll
@@ -261,7 +271,7 @@ gemm16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     tma_store_commit();
                 }
             }
-            aph ^= 1u;
+            if (++a == g.acc_bufs) a = 0, aph ^= 1u;
         }
         if (lane == 0) tma_store_wait_read<0>();  // the writes complete with the grid
         __syncwarp();
@@ -277,16 +287,18 @@ gemm16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
 }
 
-size_t pair_smem_bytes(int stages) { return 1024 + (size_t)stages * kStageBytes + kEpiBytes + 8 * (2 * (size_t)stages + 8); }
+size_t pair_smem_bytes(int BM, int BN, int stages) {
+    return 1024 + (size_t)stages * ((size_t)BM * kBK * 2 + (size_t)(BN / 2) * kBK * 2) + kEpiBytes + 8 * (2 * (size_t)stages + 8);
+}
 
-template <int DT>
+template <int DT, int HALVES, int TN>
 int launch_pair(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC, const PairArgs &g, int64_t tiles,
                 size_t smem, cudaStream_t st) {
     static std::atomic<size_t> configured{0};
     static std::atomic<int> max_clusters{0};
     if (configured.load(std::memory_order_relaxed) < smem) {
-        cudaError_t e =
-            cudaFuncSetAttribute(gemm16_pair_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm16_pair_kernel<DT, HALVES, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
         if (e != cudaSuccess) return (int)e;
         // how many pairs the device can hold at once (SMs pair up inside a GPC)
         cudaLaunchConfig_t cfg = {};
@@ -296,26 +308,36 @@ int launch_pair(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMa
         attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
         cfg.attrs = &attr, cfg.numAttrs = 1;
         int n = 0;
-        e = cudaOccupancyMaxActiveClusters(&n, gemm16_pair_kernel<DT>, &cfg);
+        e = cudaOccupancyMaxActiveClusters(&n, gemm16_pair_kernel<DT, HALVES, TN>, &cfg);
         if (e != cudaSuccess) return (int)e;
         if (n < 1) return DECA_ERR_UNSUPPORTED;
         max_clusters.store(n, std::memory_order_relaxed);
         configured.store(smem, std::memory_order_relaxed);
     }
     const int64_t pairs = tiles < max_clusters.load(std::memory_order_relaxed) ? tiles : max_clusters.load(std::memory_order_relaxed);
-    gemm16_pair_kernel<DT><<<(unsigned)(2 * pairs), kThreads, smem, st>>>(tmA, tmB, tmC, g);
+    gemm16_pair_kernel<DT, HALVES, TN><<<(unsigned)(2 * pairs), kThreads, smem, st>>>(tmA, tmB, tmC, g);
     return (int)cudaGetLastError();
+}
+
+template <int DT>
+int launch_pair_shape(int BM, int BN, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
+                      const PairArgs &g, int64_t tiles, size_t smem, cudaStream_t st) {
+    if (BM == 256) return BN == 256 ? launch_pair<DT, 2, 256>(tmA, tmB, tmC, g, tiles, smem, st)
+                                    : launch_pair<DT, 2, 128>(tmA, tmB, tmC, g, tiles, smem, st);
+    return BN == 256 ? launch_pair<DT, 1, 256>(tmA, tmB, tmC, g, tiles, smem, st)
+                     : launch_pair<DT, 1, 128>(tmA, tmB, tmC, g, tiles, smem, st);
 }
 
 }  // namespace
 
 int gemm16_pair_check(int64_t M, int64_t N, int64_t K, const deca_gemm_cfg *cfg) {
     (void)K;
-    if (cfg->BM != kCtaRows || cfg->BN != kTileN || cfg->BK != kBK) return DECA_ERR_CONFIG;
-    if (cfg->acc_bufs != 1 || !cfg->epi_smem || cfg->stream_k) return DECA_ERR_CONFIG;
-    if (cfg->stages < 2 || cfg->stages > 4 || cfg->raster < 1) return DECA_ERR_CONFIG;
-    if (pair_smem_bytes(cfg->stages) > 232448) return DECA_ERR_CONFIG;
-    const int64_t tiles = ((M + kPairRows - 1) / kPairRows) * ((N + kTileN - 1) / kTileN);
+    if ((cfg->BM != 128 && cfg->BM != 256) || (cfg->BN != 128 && cfg->BN != 256) || cfg->BK != kBK) return DECA_ERR_CONFIG;
+    if ((cfg->acc_bufs != 1 && cfg->acc_bufs != 2) || !cfg->epi_smem || cfg->stream_k) return DECA_ERR_CONFIG;
+    if (cfg->acc_bufs * (cfg->BM / 128) * cfg->BN > (int)kTmemCols) return DECA_ERR_CONFIG;
+    if (cfg->stages < 2 || cfg->stages > 8 || cfg->raster < 1) return DECA_ERR_CONFIG;
+    if (pair_smem_bytes(cfg->BM, cfg->BN, cfg->stages) > 232448) return DECA_ERR_CONFIG;
+    const int64_t tiles = ((M + 2 * cfg->BM - 1) / (2 * cfg->BM)) * ((N + cfg->BN - 1) / cfg->BN);
     if (tiles > 2147483647ll) return DECA_ERR_SHAPE;
     return DECA_OK;
 }
@@ -327,7 +349,7 @@ int gemm16_pair_launch(int dtype, const void *A, const void *B, void *C, int64_t
     {
         const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
         const uint64_t str[1] = {(uint64_t)K * 2};
-        const uint32_t box[2] = {kBK, (uint32_t)kCtaRows};
+        const uint32_t box[2] = {kBK, (uint32_t)cfg->BM};
         if ((rc = make_tmap_16bit(&tmA, dtype, A, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     }
     {
@@ -345,17 +367,18 @@ int gemm16_pair_launch(int dtype, const void *A, const void *B, void *C, int64_t
     PairArgs g;
     g.M = (int)M, g.N = (int)N, g.K = (int)K;
     g.num_kb = (int)((K + kBK - 1) / kBK);
-    g.gm = (int)((M + kPairRows - 1) / kPairRows);
-    g.gn = (int)((N + kTileN - 1) / kTileN);
+    g.gm = (int)((M + 2 * cfg->BM - 1) / (2 * cfg->BM));
+    g.gn = (int)((N + cfg->BN - 1) / cfg->BN);
     g.raster = cfg->raster < g.gm ? cfg->raster : g.gm;
     g.stages = cfg->stages;
+    g.acc_bufs = cfg->acc_bufs;
     g.status = device_status_ptr();
     if (!g.status) return (int)cudaErrorUnknown;
     const int64_t tiles = (int64_t)g.gm * g.gn;
-    const size_t smem = pair_smem_bytes(cfg->stages);
+    const size_t smem = pair_smem_bytes(cfg->BM, cfg->BN, cfg->stages);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return dtype == DECA_F16 ? launch_pair<DECA_F16>(tmA, tmB, tmC, g, tiles, smem, st)
-                             : launch_pair<DECA_BF16>(tmA, tmB, tmC, g, tiles, smem, st);
+    return dtype == DECA_F16 ? launch_pair_shape<DECA_F16>(cfg->BM, cfg->BN, tmA, tmB, tmC, g, tiles, smem, st)
+                             : launch_pair_shape<DECA_BF16>(cfg->BM, cfg->BN, tmA, tmB, tmC, g, tiles, smem, st);
 }
 
 }  // namespace deca

@@ -76,9 +76,8 @@ def check_config(cfg: GemmConfig, M: int, N: int, K: int, max_smem: int = MAX_DY
     assert cfg.BN in (64, 128, 256) and not (cfg.BM == 256 and cfg.BN == 64)
     assert cfg.cta_group in (1, 2) and cfg.acc_bufs in (1, 2)
     if cfg.cta_group == 2:
-        # CTA pairs: 512 x 256 tile, 256 rows and all 512 tensor-memory columns per CTA
-        assert cfg.BM == 256 and cfg.BN == 256 and cfg.acc_bufs == 1 and cfg.epi_smem and not cfg.stream_k
-        assert cfg.stages <= 4
+        # CTA pairs: a (2 BM) x BN tile, each CTA holds BM rows and fetches half of the B columns
+        assert cfg.BN in (128, 256) and cfg.epi_smem and not cfg.stream_k
     assert 2 <= cfg.stages <= 8
     assert cfg.raster >= 1
     assert tmem_columns(cfg) <= TMEM_COLUMNS

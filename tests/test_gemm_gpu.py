@@ -252,12 +252,25 @@ def test_stream_k_through_the_operator(native):
     ((8192, 2048, 256), 3, 4),    # 128 pair tiles: every pair runs more than one tile
 ])
 def test_cta_pair_kernel_matches_oracle(native, dtype, shape, stages, raster):
+    run_cta_pair_case(native, dtype, shape, 256, 256, stages, raster, 1)
+
+
+@pytest.mark.parametrize("tile", [(128, 256, 4, 2), (128, 128, 6, 2), (256, 128, 4, 2), (128, 256, 3, 1), (128, 128, 8, 1)],
+                         ids=lambda t: "x".join(map(str, t)))
+@pytest.mark.parametrize("shape", [(256, 128, 64), (1000, 520, 264), (1024, 1024, 512), (4096, 384, 256)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_cta_pair_smaller_tiles(native, shape, tile):
+    BM, BN, stages, acc = tile
+    run_cta_pair_case(native, "float16", shape, BM, BN, stages, 4, acc)
+
+
+def run_cta_pair_case(native, dtype, shape, BM, BN, stages, raster, acc):
     M, N, K = shape
     a_bits, b_bits = make_ab(M, N, K, dtype, seed=7)
     a, b = bits_to_torch(a_bits, dtype), bits_to_torch(b_bits, dtype)
     buf = torch.full((M + 2, N), 7.0, dtype=a.dtype, device="cuda")
     c = buf[1 : M + 1]
-    ccfg = native.GemmCfg(256, 256, 64, stages, raster, 1, 2, 1, 0)
+    ccfg = native.GemmCfg(BM, BN, 64, stages, raster, 1, 2, acc, 0)
     L = native.lib()
     assert L.deca_gemm16_check_config(native.DTYPE_CODE[dtype], M, N, K, ctypes.byref(ccfg)) == 0
     for _ in range(2):
@@ -270,7 +283,7 @@ def test_cta_pair_kernel_matches_oracle(native, dtype, shape, stages, raster):
     got = torch_to_bits(c)
     check(dtype, a_bits, b_bits, got)
     # same k order per element as the one-CTA kernel: identical bits
-    plain = run_native(native, dtype, a_bits, b_bits, dict(BM=256, BN=256, stages=3, raster=raster, acc_bufs=1))
+    plain = run_native(native, dtype, a_bits, b_bits, dict(BM=128, BN=128, stages=3, raster=raster, acc_bufs=2))
     assert np.array_equal(got, plain)
 
 
@@ -281,7 +294,9 @@ def test_cta_pair_config_rules(native):
         return L.deca_gemm16_check_config(native.F16, 4096, 4096, 4096, ctypes.byref(native.GemmCfg(*fields)))
 
     assert rc(256, 256, 64, 4, 8, 1, 2, 1, 0) == 0
-    assert rc(128, 256, 64, 4, 8, 1, 2, 1, 0) == -4  # 256 rows per CTA only
+    assert rc(128, 256, 64, 4, 8, 1, 2, 2, 0) == 0   # 128 rows per CTA, two accumulators
+    assert rc(128, 128, 64, 8, 8, 1, 2, 2, 0) == 0
+    assert rc(128, 64, 64, 4, 8, 1, 2, 2, 0) == -4   # 128 or 256 columns
     assert rc(256, 256, 64, 5, 8, 1, 2, 1, 0) == -4  # five stages do not fit
     assert rc(256, 256, 64, 3, 8, 0, 2, 1, 0) == -4  # staged epilogue only
     assert rc(256, 256, 64, 3, 8, 1, 2, 2, 0) == -4  # one accumulator (all 512 columns)
