@@ -54,6 +54,9 @@ class KernelSpec:
 
 
 def _check_tensor(t, shape, torch_dtype, name):
+    # one cheap test on the launch path; the messages below only when it fails
+    if t.shape == shape and t.dtype == torch_dtype and t.is_cuda and t.is_contiguous():
+        return
     if not t.is_cuda:
         raise ValueError(f"{name}: expected a CUDA tensor")
     if tuple(t.shape) != tuple(shape):
@@ -99,6 +102,13 @@ def load_module(path: str) -> KernelModule:
 
 
 def current_stream_ptr():
-    import torch
+    """torch's current stream on the current device as a raw handle (no Stream object is built)."""
+    global _raw_stream
+    if _raw_stream is None:
+        import torch
 
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        _raw_stream = (torch._C._cuda_getCurrentRawStream, torch.cuda.current_device)
+    return _raw_stream[0](_raw_stream[1]())
+
+
+_raw_stream = None
