@@ -548,13 +548,10 @@ int fa3_launch(const CUtensorMap &tmQ, const CUtensorMap &tmK, const CUtensorMap
     g.n_heads = B * H;
     g.status = device_status_ptr();
     if (!g.status) return (int)cudaErrorUnknown;
-    int dev = 0, sms = 0, l2 = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return (int)e;
-    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return (int)e;
-    e = cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev);
-    if (e != cudaSuccess) return (int)e;
+    DeviceInfo di;
+    const int rc = current_device_info(&di);
+    if (rc) return rc;
+    const int sms = di.sms, l2 = di.l2_bytes;
     const unsigned grid = (unsigned)(items < sms ? items : sms);
     g.sec_heads = g.n_heads;
     if (causal) g.sec_heads = choose_sec_heads((int)grid, g.n_heads, g.n_pairs, 2ll * S_kv * D * 2, l2);

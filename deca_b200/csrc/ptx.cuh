@@ -9,6 +9,30 @@
 
 namespace deca {
 
+// Attributes of the current device, queried once per device (the launch paths ask on every call).
+struct DeviceInfo {
+    int sms, l2_bytes;
+};
+inline int current_device_info(DeviceInfo *out) {
+    static DeviceInfo info[64];
+    static bool known[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return DECA_ERR_UNSUPPORTED;
+    if (!known[dev]) {  // a race only repeats the query: both writers store the same values
+        DeviceInfo d;
+        e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaDeviceGetAttribute(&d.l2_bytes, cudaDevAttrL2CacheSize, dev);
+        if (e != cudaSuccess) return (int)e;
+        info[dev] = d;
+        known[dev] = true;
+    }
+    *out = info[dev];
+    return 0;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
