@@ -132,3 +132,32 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(n, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="no fallback"):
         n.lib()
+
+
+def test_gemm_default_config_and_stream_k_plan():
+    """Host-side choices of the GEMM: default tiles cover the SMs where they can, and the Python
+    mirror of the stream-K plan gives equal shares that add up to the split tiles' k blocks."""
+    from deca_b200.kernels.gemm_b200 import GemmConfig, check_config, default_config, stream_k_plan
+
+    assert (default_config(4096, 4096, 4096).BM, default_config(4096, 4096, 4096).BN) == (256, 256)
+    assert (default_config(2048, 2048, 2048).BM, default_config(2048, 2048, 2048).BN) == (128, 256)
+    assert default_config(1024, 1024, 1024).BN == 64  # 128 tiles of 128 x 64 beat 32 of 128 x 256
+    assert default_config(8192, 64, 512).BN == 64
+    for shape in ((4096, 4096, 4096), (300, 40, 128), (1536, 1536, 1536), (65536, 8192, 8192)):
+        check_config(default_config(*shape), *shape)
+
+    cfg = GemmConfig(BM=256, BN=256, stages=3, acc_bufs=1, stream_k=True)
+    grid, dp_tiles, units = stream_k_plan(cfg, 4096, 4096, 4096)
+    assert (grid, dp_tiles, units) == (148, 0, 256 * 64)  # 256 tiles: the one full wave joins the remainder
+    assert stream_k_plan(cfg, 8192, 8192, 8192) is None  # 1024 tiles fill 6.9 waves
+    grid, dp_tiles, units = stream_k_plan(GemmConfig(BM=128, BN=128, stages=3, stream_k=True), 2560, 2560, 256)
+    assert (grid, dp_tiles, units) == (148, 148, 252 * 4)  # 400 tiles: one whole wave, then 252 tiles split
+    assert stream_k_plan(GemmConfig(BM=128, BN=128, stages=3, stream_k=True), 512, 512, 512) is None  # too little work
+    # pair configs: tile shapes and tensor-memory budget
+    check_config(GemmConfig(BM=128, BN=256, stages=4, acc_bufs=2, cta_group=2), 2048, 2048, 2048)
+    import pytest
+
+    with pytest.raises(AssertionError):
+        check_config(GemmConfig(BM=256, BN=256, stages=3, acc_bufs=2, cta_group=2), 4096, 4096, 4096)
+    with pytest.raises(AssertionError):
+        check_config(GemmConfig(BM=128, BN=64, stages=4, acc_bufs=2, cta_group=2), 4096, 4096, 4096)
