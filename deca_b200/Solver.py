@@ -150,7 +150,7 @@ def solve_rowwise(arch, op: str, M: int, N: int, type_size: int = 2, twopass_min
     n = BitVecVal(N, 32)
     s.add(Or([tpr == v for v in (32, 64, 128, 256, 512, 1024)]))
     s.add(Or([rpb == v for v in (1, 2, 3, 4, 8, 15, 16)]))
-    s.add(Or(vec == 4, vec == 8))
+    s.add(Or(vec == 4, vec == 8) if N % 4 == 0 else vec == 2)  # 4-byte accesses only for rows that need them
     s.add(ULE(mode, 2))
     s.add(Or(unroll == 1, unroll == 2, unroll == 3, unroll == 4))
     s.add(ULE(hint, 1))

@@ -26,8 +26,14 @@ namespace {
 
 template <int WORDS, bool HINT>
 __device__ __forceinline__ void load_words(uint32_t (&d)[WORDS], const void *p) {
-    static_assert(WORDS == 4 || WORDS == 2, "16- or 8-byte accesses");
-    if constexpr (WORDS == 4) {
+    static_assert(WORDS == 4 || WORDS == 2 || WORDS == 1, "16-, 8- or 4-byte accesses");
+    if constexpr (WORDS == 1) {
+        if constexpr (HINT) {
+            asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(d[0]) : "l"(p));
+        } else {
+            d[0] = *reinterpret_cast<const uint32_t *>(p);
+        }
+    } else if constexpr (WORDS == 4) {
         if constexpr (HINT) {
             asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                          : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
@@ -50,7 +56,13 @@ __device__ __forceinline__ void load_words(uint32_t (&d)[WORDS], const void *p) 
 
 template <int WORDS, bool HINT>
 __device__ __forceinline__ void store_words(void *p, const uint32_t (&d)[WORDS]) {
-    if constexpr (WORDS == 4) {
+    if constexpr (WORDS == 1) {
+        if constexpr (HINT) {
+            asm volatile("st.global.cs.u32 [%0], %1;" ::"l"(p), "r"(d[0]) : "memory");
+        } else {
+            *reinterpret_cast<uint32_t *>(p) = d[0];
+        }
+    } else if constexpr (WORDS == 4) {
         if constexpr (HINT) {
             asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(d[0]), "r"(d[1]), "r"(d[2]),
                          "r"(d[3])
@@ -423,8 +435,12 @@ int launch_vec(const deca_row_cfg &c, int chunks, const RowArgs &a, unsigned gri
     if (c.vec == 8)
         return c.hint ? launch_mode<OP, DT, 4, true>(c, chunks, a, grid, threads, st)
                       : launch_mode<OP, DT, 4, false>(c, chunks, a, grid, threads, st);
-    return c.hint ? launch_mode<OP, DT, 2, true>(c, chunks, a, grid, threads, st)
-                  : launch_mode<OP, DT, 2, false>(c, chunks, a, grid, threads, st);
+    if (c.vec == 4)
+        return c.hint ? launch_mode<OP, DT, 2, true>(c, chunks, a, grid, threads, st)
+                      : launch_mode<OP, DT, 2, false>(c, chunks, a, grid, threads, st);
+    // rows whose length is only a multiple of 2: 4-byte accesses
+    return c.hint ? launch_mode<OP, DT, 1, true>(c, chunks, a, grid, threads, st)
+                  : launch_mode<OP, DT, 1, false>(c, chunks, a, grid, threads, st);
 }
 
 }  // namespace
@@ -444,7 +460,7 @@ extern "C" int deca_rowwise_check_config(int op, int dtype, int64_t M, int64_t N
     if (M <= 0 || N <= 0 || N > (1ll << 30)) return DECA_ERR_SHAPE;
     if (cfg->mode == DECA_ROW_TMA) return rowwise_tma_check(op, M, N, *cfg);
     if (cfg->mode != DECA_ROW_REG && cfg->mode != DECA_ROW_TWOPASS) return DECA_ERR_CONFIG;
-    if (cfg->vec != 8 && cfg->vec != 4) return DECA_ERR_CONFIG;
+    if (cfg->vec != 8 && cfg->vec != 4 && cfg->vec != 2) return DECA_ERR_CONFIG;
     if (N % cfg->vec != 0) return DECA_ERR_CONFIG;
     if (cfg->threads_per_row < 32 || cfg->threads_per_row % 32 != 0) return DECA_ERR_CONFIG;
     if (cfg->rows_per_block < 1) return DECA_ERR_CONFIG;
@@ -475,7 +491,7 @@ extern "C" int deca_rowwise_default_config(int op, int dtype, int64_t M, int64_t
     if (!out) return DECA_ERR_NULL;
     if (M <= 0 || N <= 0) return DECA_ERR_SHAPE;
     deca_row_cfg c;
-    c.vec = (N % 8 == 0) ? 8 : 4;
+    c.vec = (N % 8 == 0) ? 8 : (N % 4 == 0 ? 4 : 2);
     c.hint = 1;  // every byte is touched once: keep it out of L1 and stream the stores
     c.unroll = 1;
     c.mode = DECA_ROW_REG;

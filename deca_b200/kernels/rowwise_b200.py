@@ -91,7 +91,7 @@ def check_config(cfg: RowConfig, op: str, M: int, N: int, dtype: str) -> None:
         assert num_chunks(cfg, N) <= MAX_TMA_CHUNKS
         assert tma_smem_bytes(cfg, op, N) <= MAX_DYN_SMEM
         return
-    assert cfg.vec in (4, 8) and N % cfg.vec == 0
+    assert cfg.vec in (2, 4, 8) and N % cfg.vec == 0
     assert cfg.threads_per_row % 32 == 0 and cfg.threads_per_row >= 32 and cfg.threads <= 1024
     assert cfg.rows_per_block >= 1 and M % cfg.rows_per_block == 0
     assert cfg.unroll in (1, 2, 4)

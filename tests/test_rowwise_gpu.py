@@ -68,7 +68,8 @@ def check(op, dtype, x_bits, w_bits, y_bits, eps=1e-6):
         assert np.mean(err <= rowwise_allowed(ref32, dtype)) > 0.995
 
 
-SHAPES = [(4, 4096), (3, 1000), (5, 8), (148 * 3, 1024), (64, 8192), (8, 32000), (2, 128256), (16, 2048), (7, 4104)]
+SHAPES = [(4, 4096), (3, 1000), (5, 8), (148 * 3, 1024), (64, 8192), (8, 32000), (2, 128256), (16, 2048), (7, 4104),
+          (6, 1002), (9, 50), (3, 4098), (2, 2)]  # the last four: rows that are only a multiple of 2 long
 
 
 @pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
