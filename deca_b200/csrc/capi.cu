@@ -7,6 +7,8 @@ namespace deca {
 
 __device__ DeviceStatus g_device_status = {};
 
+constexpr unsigned int kSelfTestSite = 0x7E57u;  // `where` reported by deca_selftest_bounded_wait
+
 DeviceStatus *device_status_ptr() {
     // The symbol has one address per device; cache them.
     static std::mutex mu;
@@ -22,7 +24,44 @@ DeviceStatus *device_status_ptr() {
     return ptrs[dev];
 }
 
+// Self-test of the bounded-wait path the pipelined kernels rely on, without any of their
+// machinery: thread 0 waits on an mbarrier that nothing ever arrives on, with a short limit;
+// when the limit passes it raises the CTA's abort flag and reports the timeout exactly as the
+// kernels do.  Thread 32 waits on the same barrier with the kernels' default limit and has to
+// leave through the abort flag.  Both record how long they waited (microseconds) in the detail
+// words 0 and 1.  The kernel returns normally; nothing traps or spins without a bound.
+__global__ void bounded_wait_selftest_kernel(DeviceStatus *st, unsigned long long limit_ns) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ uint32_t abort_flag;
+    const uint32_t bar_addr = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(bar_addr, 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 || threadIdx.x == 32) {
+        const uint64_t t0 = globaltimer_ns();
+        const bool done = mbar_wait(bar_addr, 0, &abort_flag, threadIdx.x == 0 ? (uint64_t)limit_ns : kWaitLimitNs);
+        const uint64_t waited_us = (globaltimer_ns() - t0) / 1000ull;
+        if (!done && threadIdx.x == 0) {
+            abort_flag = 1;
+            report_timeout(st, kSelfTestSite);
+        }
+        st->detail[threadIdx.x == 0 ? 0 : 1] = (unsigned int)(waited_us > 0xFFFFFFFFull ? 0xFFFFFFFFull : waited_us);
+    }
+    __syncthreads();
+}
+
 }  // namespace deca
+
+extern "C" int deca_selftest_bounded_wait(unsigned int limit_us, void *stream) {
+    if (limit_us < 1 || limit_us > 100000) return DECA_ERR_SHAPE;  // 1 us .. 100 ms
+    deca::DeviceStatus *p = deca::device_status_ptr();
+    if (!p) return (int)cudaErrorUnknown;
+    deca::bounded_wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(p, 1000ull * limit_us);
+    return (int)cudaGetLastError();
+}
 
 extern "C" int deca_last_device_status(int *code, int *where, int *block, int clear) {
     deca::DeviceStatus *p = deca::device_status_ptr();

@@ -493,12 +493,8 @@ template <int D, int BC, bool PTMEM>
 int launch_fa2(const CUtensorMap &tmQ, const CUtensorMap &tmK, const CUtensorMap &tmV, const CUtensorMap &tmO,
                const PeerMaps &peers,
                const Fa2Args &g, dim3 grid, size_t smem, cudaStream_t st) {
-    static std::atomic<size_t> configured{0};
-    if (configured.load(std::memory_order_relaxed) < smem) {
-        cudaError_t e = cudaFuncSetAttribute(fa_fwd2_kernel<D, BC, PTMEM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured.store(smem, std::memory_order_relaxed);
-    }
+    static SmemLimitCache configured;
+    if (int rc = ensure_dynamic_smem(fa_fwd2_kernel<D, BC, PTMEM>, smem, configured)) return rc;
     fa_fwd2_kernel<D, BC, PTMEM><<<grid, kThreads2, smem, st>>>(tmQ, tmK, tmV, tmO, peers, g);
     return (int)cudaGetLastError();
 }

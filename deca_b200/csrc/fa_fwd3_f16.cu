@@ -448,12 +448,8 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 template <int D>
 int launch_fa3(const CUtensorMap &tmQ, const CUtensorMap &tmK, const CUtensorMap &tmV, const CUtensorMap &tmO,
                const PeerMaps &peers, const Fa3Args &g, unsigned grid, size_t smem, cudaStream_t st) {
-    static std::atomic<size_t> configured{0};
-    if (configured.load(std::memory_order_relaxed) < smem) {
-        cudaError_t e = cudaFuncSetAttribute(fa_fwd3_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured.store(smem, std::memory_order_relaxed);
-    }
+    static SmemLimitCache configured;
+    if (int rc = ensure_dynamic_smem(fa_fwd3_kernel<D>, smem, configured)) return rc;
     fa_fwd3_kernel<D><<<grid, kThreads3, smem, st>>>(tmQ, tmK, tmV, tmO, peers, g);
     return (int)cudaGetLastError();
 }

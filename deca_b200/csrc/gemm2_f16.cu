@@ -294,27 +294,35 @@ size_t pair_smem_bytes(int BM, int BN, int stages) {
 template <int DT, int HALVES, int TN>
 int launch_pair(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC, const PairArgs &g, int64_t tiles,
                 size_t smem, cudaStream_t st) {
-    static std::atomic<size_t> configured{0};
-    static std::atomic<int> max_clusters{0};
-    if (configured.load(std::memory_order_relaxed) < smem) {
-        cudaError_t e = cudaFuncSetAttribute(gemm16_pair_kernel<DT, HALVES, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        // how many pairs the device can hold at once (SMs pair up inside a GPC)
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2), cfg.blockDim = dim3(kThreads), cfg.dynamicSmemBytes = smem;
-        cudaLaunchAttribute attr;
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
-        cfg.attrs = &attr, cfg.numAttrs = 1;
-        int n = 0;
-        e = cudaOccupancyMaxActiveClusters(&n, gemm16_pair_kernel<DT, HALVES, TN>, &cfg);
-        if (e != cudaSuccess) return (int)e;
-        if (n < 1) return DECA_ERR_UNSUPPORTED;
-        max_clusters.store(n, std::memory_order_relaxed);
-        configured.store(smem, std::memory_order_relaxed);
+    // per device: the shared-memory limit set for this instance and how many pairs the device can
+    // hold at once with it (SMs pair up inside a GPC)
+    static std::atomic<size_t> configured[64];
+    static std::atomic<int> max_clusters[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return DECA_ERR_UNSUPPORTED;
+    if (configured[dev].load(std::memory_order_acquire) < smem) {
+        std::lock_guard<std::mutex> lock(smem_limit_mutex());
+        if (configured[dev].load(std::memory_order_relaxed) < smem) {
+            e = cudaFuncSetAttribute(gemm16_pair_kernel<DT, HALVES, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2), cfg.blockDim = dim3(kThreads), cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr;
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+            cfg.attrs = &attr, cfg.numAttrs = 1;
+            int n = 0;
+            e = cudaOccupancyMaxActiveClusters(&n, gemm16_pair_kernel<DT, HALVES, TN>, &cfg);
+            if (e != cudaSuccess) return (int)e;
+            if (n < 1) return DECA_ERR_UNSUPPORTED;
+            max_clusters[dev].store(n, std::memory_order_relaxed);
+            configured[dev].store(smem, std::memory_order_release);
+        }
     }
-    const int64_t pairs = tiles < max_clusters.load(std::memory_order_relaxed) ? tiles : max_clusters.load(std::memory_order_relaxed);
+    const int64_t max_pairs = max_clusters[dev].load(std::memory_order_relaxed);
+    const int64_t pairs = tiles < max_pairs ? tiles : max_pairs;
     gemm16_pair_kernel<DT, HALVES, TN><<<(unsigned)(2 * pairs), kThreads, smem, st>>>(tmA, tmB, tmC, g);
     return (int)cudaGetLastError();
 }

@@ -5,6 +5,9 @@
 
 #include <cuda.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "common.cuh"
 
 namespace deca {
@@ -30,6 +33,33 @@ inline int current_device_info(DeviceInfo *out) {
         known[dev] = true;
     }
     *out = info[dev];
+    return 0;
+}
+
+// The dynamic shared-memory limit of a kernel is an attribute of (function, device).  One of
+// these per kernel instance remembers, per device ordinal, the largest size already set; raising
+// it happens under a mutex so that concurrent host threads can only ever raise the limit.
+struct SmemLimitCache {
+    std::atomic<size_t> bytes[64];
+};
+inline std::mutex &smem_limit_mutex() {
+    static std::mutex mu;
+    return mu;
+}
+template <typename Kernel>
+inline int ensure_dynamic_smem(Kernel kernel, size_t smem, SmemLimitCache &cache, int *device = nullptr) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return DECA_ERR_UNSUPPORTED;
+    if (device) *device = dev;
+    std::atomic<size_t> &have = cache.bytes[dev];
+    if (have.load(std::memory_order_acquire) >= smem) return 0;
+    std::lock_guard<std::mutex> lock(smem_limit_mutex());
+    if (have.load(std::memory_order_relaxed) >= smem) return 0;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    have.store(smem, std::memory_order_release);
     return 0;
 }
 
@@ -81,7 +111,8 @@ constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s: far beyo
 // Waits for the phase with `parity` of `bar` to complete.  Gives up (returns false) when another
 // thread of the CTA has raised `*abort_flag` or when the time limit passes, so that a protocol
 // error ends in an error status instead of a hang.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
 #pragma unroll 1
     for (int i = 0; i < 2048; ++i)
         if (mbar_try_wait(bar, parity)) return true;
@@ -92,7 +123,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag != 0) return false;
-        if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+        if (globaltimer_ns() - t0 > limit_ns) return false;
     }
 }
 

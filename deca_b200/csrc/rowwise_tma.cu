@@ -283,12 +283,8 @@ size_t tma_smem_bytes(int op, int ng, int stages_in, uint32_t row_pitch) {
 
 template <typename K, K kernel>
 int launch_tma(const RowTmaArgs &args, unsigned grid, unsigned threads, size_t smem, cudaStream_t st) {
-    static std::atomic<size_t> configured{0};
-    if (configured.load(std::memory_order_relaxed) < smem) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured.store(smem, std::memory_order_relaxed);
-    }
+    static SmemLimitCache configured;
+    if (int rc = ensure_dynamic_smem(kernel, smem, configured)) return rc;
     kernel<<<grid, threads, smem, st>>>(args);
     return (int)cudaGetLastError();
 }

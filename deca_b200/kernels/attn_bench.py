@@ -1,86 +1,57 @@
-"""Timing / reference helpers shared by the benchmarks (same surface as the reference's
-src/kernels/attn_bench.py): CUDA-event timer, interleaved timer, attention inputs, the SDPA
-baseline, the FLOP formula and the FlashAttention-2 paper grid."""
+"""Attention benchmark helpers behind the names the reference's CLIs and RuntimeMod import from
+src/kernels/attn_bench.py: the sweep grid (:17-27), the work formula (:30-32), the timers
+(:35-70, :94-100; implemented in ``timing.py``), seeded inputs (:73-78) and the SDPA baseline
+(:81-91)."""
+
+from __future__ import annotations
 
 import math
-import time
-from typing import Callable
 
-import torch
-import torch.nn.functional as F
-from torch.nn.attention import SDPBackend, sdpa_kernel
+from .timing import bench_cuda, bench_interleaved  # noqa: F401  (part of this module's surface)
 
-# FlashAttention-2 paper setup: hidden = 2048, batch * seqlen = 16k.
-FA_SEQLENS = [512, 1024, 2048, 4096, 8192, 16384]
-FA_HEADDIM_HEADS = [(64, 32), (128, 16)]
+# The FlashAttention-2 paper grid: 16 Ki tokens per batch, model width 2048 split into heads of
+# 64 or 128, sequence lengths 512 ... 16 Ki.
+TOKENS_PER_BATCH = 16384
+MODEL_WIDTH = 2048
+HEAD_DIMS = (64, 128)
+SEQ_LENS = tuple(1 << p for p in range(9, 15))
 
 
 def standard_shapes():
-    """Returns a list of (B, H, S, D)."""
-    return [(16384 // S, H, S, D) for D, H in FA_HEADDIM_HEADS for S in FA_SEQLENS]
+    """[(B, H, S, D)] of the sweep, head dim outermost."""
+    return [(TOKENS_PER_BATCH // S, MODEL_WIDTH // D, S, D) for D in HEAD_DIMS for S in SEQ_LENS]
 
 
 def attn_flops(B: int, H: int, S_q: int, S_kv: int, D: int, causal: bool = False) -> float:
-    flops = 4.0 * B * H * S_q * S_kv * D
-    return flops / 2 if causal else flops
-
-
-def bench_cuda(fn: Callable[[], None], warmup_s: float = 0.3, measure_s: float = 0.3, min_iters: int = 20) -> float:
-    """Median time of ``fn`` in seconds over per-call CUDA events, after a time-based warm-up."""
-    fn()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    while time.perf_counter() - t0 < warmup_s:
-        fn()
-        torch.cuda.synchronize()
-    probe = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-    probe[0].record()
-    fn()
-    probe[1].record()
-    probe[1].synchronize()
-    per_call = max(probe[0].elapsed_time(probe[1]) / 1e3, 1e-6)
-    iters = max(min_iters, int(measure_s / per_call))
-    times = []
-    for _ in range(iters):
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        fn()
-        end.record()
-        end.synchronize()
-        times.append(start.elapsed_time(end) / 1e3)
-    times.sort()
-    return times[len(times) // 2]
-
-
-def bench_interleaved(fns: dict, rounds: int = 3) -> dict:
-    """Times several callables alternately; returns the median per name (seconds)."""
-    samples = {name: [] for name in fns}
-    for _ in range(rounds):
-        for name, fn in fns.items():
-            samples[name].append(bench_cuda(fn))
-    return {name: sorted(ts)[len(ts) // 2] for name, ts in samples.items()}
-
-
-def make_qkv(B: int, H: int, S_q: int, S_kv: int, D: int, dtype=torch.float16, seed: int = 0):
-    g = torch.Generator(device="cuda").manual_seed(seed)
-    q = torch.randn(B, H, S_q, D, device="cuda", dtype=dtype, generator=g)
-    k = torch.randn(B, H, S_kv, D, device="cuda", dtype=dtype, generator=g)
-    v = torch.randn(B, H, S_kv, D, device="cuda", dtype=dtype, generator=g)
-    return q, k, v
-
-
-def sdpa_flash(q, k, v, causal: bool = False, scale: float | None = None):
-    with sdpa_kernel(SDPBackend.FLASH_ATTENTION):
-        return F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale)
-
-
-def bench_sdpa_flash(B, H, S_q, S_kv, D, causal=False, dtype=torch.float16):
-    """Returns (seconds, TFLOPS) of torch SDPA restricted to the flash backend."""
-    q, k, v = make_qkv(B, H, S_q, S_kv, D, dtype)
-    with sdpa_kernel(SDPBackend.FLASH_ATTENTION):
-        t = bench_cuda(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=causal))
-    return t, attn_flops(B, H, S_q, S_kv, D, causal) / t / 1e12
+    """Two GEMMs of 2 * S_q * S_kv * D flops per head; a causal mask halves the count."""
+    return 4.0 * B * H * S_q * S_kv * D * (0.5 if causal else 1.0)
 
 
 def default_scale(D: int) -> float:
     return 1.0 / math.sqrt(D)
+
+
+def make_qkv(B: int, H: int, S_q: int, S_kv: int, D: int, dtype=None, seed: int = 0):
+    """Standard-normal Q, K, V on the GPU from one seeded CUDA generator (drawn in that order)."""
+    import torch
+
+    dtype = dtype or torch.float16
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    return tuple(torch.randn(B, H, S, D, device="cuda", dtype=dtype, generator=gen) for S in (S_q, S_kv, S_kv))
+
+
+def sdpa_flash(q, k, v, causal: bool = False, scale: float | None = None):
+    """torch's scaled_dot_product_attention restricted to its flash backend: the baseline and the
+    correctness reference of the attention operator."""
+    import torch.nn.functional as F
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    with sdpa_kernel(SDPBackend.FLASH_ATTENTION):
+        return F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale)
+
+
+def bench_sdpa_flash(B, H, S_q, S_kv, D, causal=False, dtype=None):
+    """(seconds, TFLOPS) of the SDPA-flash baseline on fresh seeded inputs."""
+    q, k, v = make_qkv(B, H, S_q, S_kv, D, dtype)
+    seconds = bench_cuda(lambda: sdpa_flash(q, k, v, causal=causal))
+    return seconds, attn_flops(B, H, S_q, S_kv, D, causal) / seconds / 1e12

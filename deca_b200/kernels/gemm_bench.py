@@ -1,40 +1,40 @@
-"""Shapes, inputs and baselines of the 16-bit tensor-core GEMM C = A @ B (same surface as the
-reference's src/kernels/gemm_bench.py).  A[M, K], B[K, N], C[M, N] are row-major; accumulation
-is fp32."""
+"""GEMM benchmark helpers behind the names the reference's CLI imports from
+src/kernels/gemm_bench.py: the square sweep (:14-19), the work formula (:22-23), seeded inputs
+(:26-31) and the torch baseline (:34-44).  A[M, K], B[K, N], C[M, N] row-major, fp32 accumulation."""
 
-import torch
+from __future__ import annotations
 
-from .attn_bench import bench_cuda, bench_interleaved  # noqa: F401  (re-exported)
+from .timing import bench_cuda, bench_interleaved  # noqa: F401  (part of this module's surface)
 
-# Square GEMMs from 2K to 16K in steps of 2K.
-SQUARE_SIZES = list(range(2048, 16384 + 1, 2048))
+SWEEP_FIRST, SWEEP_LAST, SWEEP_STEP = 2048, 16384, 2048
 
 
 def standard_shapes():
-    """Returns a list of (M, N, K)."""
-    return [(n, n, n) for n in SQUARE_SIZES]
+    """[(n, n, n)] for n = 2048, 4096, ..., 16384."""
+    return [(n, n, n) for n in range(SWEEP_FIRST, SWEEP_LAST + 1, SWEEP_STEP)]
 
 
 def gemm_flops(M: int, N: int, K: int) -> float:
     return 2.0 * M * N * K
 
 
-def make_inputs(M: int, N: int, K: int, seed: int = 0, dtype=torch.float16):
-    """Returns (a, b) with unit-variance 16-bit entries."""
-    g = torch.Generator(device="cuda").manual_seed(seed)
-    a = torch.randn(M, K, device="cuda", dtype=dtype, generator=g)
-    b = torch.randn(K, N, device="cuda", dtype=dtype, generator=g)
-    return a, b
+def make_inputs(M: int, N: int, K: int, seed: int = 0, dtype=None):
+    """Standard-normal A then B on the GPU from one seeded CUDA generator."""
+    import torch
+
+    dtype = dtype or torch.float16
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    return tuple(torch.randn(*shape, device="cuda", dtype=dtype, generator=gen) for shape in ((M, K), (K, N)))
 
 
 def torch_ref(inputs):
-    """torch (cuBLAS) baseline."""
+    """The cuBLAS baseline (torch.matmul on the 16-bit inputs)."""
     a, b = inputs
     return a @ b
 
 
 def bench_torch(M: int, N: int, K: int):
-    """Returns (seconds, TFLOPS) of torch.matmul."""
+    """(seconds, TFLOPS) of torch.matmul on fresh seeded inputs."""
     inputs = make_inputs(M, N, K)
-    t = bench_cuda(lambda: torch_ref(inputs))
-    return t, gemm_flops(M, N, K) / t / 1e12
+    seconds = bench_cuda(lambda: torch_ref(inputs))
+    return seconds, gemm_flops(M, N, K) / seconds / 1e12

@@ -78,6 +78,7 @@ def lib() -> ctypes.CDLL:
         ip = ctypes.POINTER(ci)
         L.deca_last_device_status.argtypes = [ip, ip, ip, ci]
         L.deca_device_status_words.argtypes = [ctypes.POINTER(ctypes.c_uint), ci]
+        L.deca_selftest_bounded_wait.argtypes = [ctypes.c_uint, vp]
         _lib = L
     return _lib
 
