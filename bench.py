@@ -261,6 +261,11 @@ class GemmWorkload(Workload):
         self.kernel = f"gemm16 {self.cfg}"
         self.env = env
 
+    def reference_kernel_groups(self, rk):
+        a, b, c = self.sets[0]
+        cands = [(e, (a, b, c)) for e in rk.entries("gemm", (self.M, self.N, self.K))]
+        return [("gemm", cands, self.op.num_flops)] if cands and not self.shard_m else []
+
     # ---- e2e: pinned host A, B -> device -> operator calls on row chunks -> pinned host C ----
     def _e2e_setup(self):
         import torch
@@ -456,6 +461,12 @@ class AttentionWorkload(Workload):
         self.kernel = f"fa_fwd {'causal' if self.causal else 'non-causal'} {self.cfg}"
         self.env = env
 
+    def reference_kernel_groups(self, rk):
+        q, k, v, o = self.sets[0]
+        shape = (self.B, self.H, self.S, self.S, self.D)
+        cands = [(e, (q, k, v, o)) for e in rk.entries("flash_attn", shape, causal=self.causal)]
+        return [("flash_attn", cands, self.op.num_flops)] if cands and not self.shard_bh else []
+
     def step_e2e(self):
         import torch
 
@@ -633,6 +644,17 @@ class RowwiseWorkload(Workload):
         self.dominant_units = self.ops[0][1].num_bytes
         self.kernel = f"rowwise_reg softmax/rmsnorm {self.ops[0][1].default_config()}"
         self.env = env
+
+    def reference_kernel_groups(self, rk):
+        groups = []
+        for (kind, dt), op in self.ops:
+            x, w = self.dev[dt]
+            tensors = (x, self.out[(kind, dt)]) if kind == "softmax" else (x, w, self.out[(kind, dt)])
+            cands = [(e, tensors) for e in rk.entries("rowwise", (self.M, self.N), op=kind, dtype=dt)]
+            if not cands:
+                return []
+            groups.append((f"{kind} {dt}", cands, op.num_bytes))
+        return groups
 
     def _e2e_setup(self):
         import torch
@@ -853,9 +875,48 @@ def measure_record(wl, env, peaks, seconds, use_graph, bursts=4):
         base_value = wl.to_value(wl.units * rounds_base * bursts * n / (base_ms / 1e3))
         rec["comparison"] = {"what": wl.baseline_name + ", timed alternately on the same tensors", "value": base_value,
                              "unit": wl.unit, "ratio": value / base_value}
+    if env.world == 1:
+        rec["comparison_reference_kernels"] = reference_kernels_leg(wl, value)
     if hasattr(wl, "verify"):
         rec["verified"] = wl.verify()
     return rec
+
+
+def reference_kernels_leg(wl, value, seconds=0.25):
+    """The reference's own mma.sync / cp.async kernels (generated by its TIR generators, prebuilt
+    for sm_100a) on the same tensors, beside the timed region: per launch of the workload the
+    fastest of the prebuilt configs.  A baseline and a sanity check, never the thing measured."""
+    import torch
+
+    try:
+        from oracle import ref_kernels as rk
+
+        why = rk.unavailable_reason()
+    except Exception as e:  # noqa: BLE001
+        why = f"{type(e).__name__}: {str(e)[-120:]}"
+    if why:
+        return {"unavailable": why}
+    groups = wl.reference_kernel_groups(rk) if hasattr(wl, "reference_kernel_groups") else []
+    if not groups:
+        return {"unavailable": "no prebuilt reference kernel for this shape"}
+    total_s, total_units, picks = 0.0, 0.0, []
+    for label, cands, units in groups:
+        best = None
+        for entry, tensors in cands:
+            launch = rk.bind(entry, *tensors)
+            launch()
+            torch.cuda.synchronize()
+            t1 = max(time_ms(lambda r: [launch() for _ in range(r)], 2) / 2, 1e-3)
+            reps = max(3, int(seconds * 1e3 / t1))
+            t = time_ms(lambda r: [launch() for _ in range(r)], reps) / reps / 1e3
+            if best is None or t < best[0]:
+                best = (t, entry["config_str"])
+        total_s += best[0]
+        total_units += units
+        picks.append(f"{label}: {best[1]}")
+    ref_value = wl.to_value(total_units / total_s)
+    return {"what": "the reference's own generated kernels (mma.sync, prebuilt for sm_100a), best prebuilt config, same tensors",
+            "configs": picks, "value": ref_value, "unit": wl.unit, "ratio": value / ref_value}
 
 
 def host_link_probe(env, nbytes=256 << 20):
