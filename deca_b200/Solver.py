@@ -30,9 +30,10 @@ def solve_gemm_tc(arch, M: int, N: int, K: int, type_size: int = 2, count: int =
                   acc_splits: int = 1):
     """Enumerates 16-bit tensor-core GEMM tile configurations (see ``GemmConfig``).
 
-    arch supplies ``max_dyn_smem_per_block``, ``tmem_columns`` and ``sm_nums``.  ``acc_f16`` and
-    ``acc_splits`` are accepted for call-site compatibility and change nothing: the tcgen05 kernel
-    always accumulates in fp32, which also serves an operator built with ``acc="fp16"``.
+    arch supplies ``max_dyn_smem_per_block``, ``tmem_columns`` and ``sm_nums``.  ``acc_f16`` asks
+    for configs with fp16 accumulators (one-CTA tiles, no stream-K: an fp16 accumulator takes the
+    same tensor-memory columns as an fp32 one, so the tile space is otherwise the same);
+    ``acc_splits`` is accepted for call-site compatibility (the accumulator is a single one).
     """
     from .kernels.gemm_b200 import SMEM_RESERVED, GemmConfig, check_config, stream_k_plan
 
@@ -64,7 +65,7 @@ def solve_gemm_tc(arch, M: int, N: int, K: int, type_size: int = 2, count: int =
             if ras > 1 and ras > gm_of[vals[0]]:
                 continue
             cfg = GemmConfig(BM=vals[0], BN=vals[1], BK=64, stages=vals[2], raster=ras, epi_smem=bool(vals[3]),
-                             cta_group=1, acc_bufs=vals[4])
+                             cta_group=1, acc_bufs=vals[4], acc_f16=acc_f16)
             try:
                 check_config(cfg, M, N, K)
             except AssertionError:
@@ -73,12 +74,14 @@ def solve_gemm_tc(arch, M: int, N: int, K: int, type_size: int = 2, count: int =
             # the stream-K form of the config, where whole tiles would leave a quarter of a wave idle
             tiles = gm_of[vals[0]] * -(-N // vals[1])
             sms = arch.sm_nums
-            if ras == 8 and cfg.epi_smem and tiles / (-(-tiles // sms) * sms) < 0.75:
+            if not acc_f16 and ras == 8 and cfg.epi_smem and tiles / (-(-tiles // sms) * sms) < 0.75:
                 sk = GemmConfig(**{**cfg.as_dict(), "stream_k": True})
                 if stream_k_plan(sk, M, N, K, sms) is not None:
                     results.append(sk)
     # CTA pairs (tcgen05 cta_group::2): (2 BM) x BN tiles whose CTAs fetch half of the B columns each
     for bm_, bn_, acc_ in ((256, 256, 1), (128, 256, 2), (128, 256, 1), (256, 128, 2), (128, 128, 2)):
+        if acc_f16:
+            break
         if -(-M // (2 * bm_)) * -(-N // bn_) < 8 or bn_ > max(2 * N - 1, 128):
             continue
         for st in (3, 4, 6, 8):

@@ -45,18 +45,12 @@ def is_up_to_date() -> bool:
     return all(os.path.getmtime(p) <= t for p in _sources() + _headers() + [os.path.abspath(__file__)])
 
 
-def _extra_defs():
-    """Extra -D flags from the environment (DECA_NVCC_DEFS="-DDECA_FA_PROFILE ..."), for one-off
-    instrumented builds; the default build has none."""
-    return os.environ.get("DECA_NVCC_DEFS", "").split()
-
-
 def _compile(src: str, verbose: bool) -> str:
     obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
     hdr_t = max([os.path.getmtime(h) for h in _headers()] + [os.path.getmtime(os.path.abspath(__file__))])
     if os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src), hdr_t):
         return obj
-    cmd = ["nvcc", *NVCC_FLAGS, *_extra_defs(), *(["-Xptxas", "-v"] if verbose else []), "-c", src, "-o", obj]
+    cmd = ["nvcc", *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-c", src, "-o", obj]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)

@@ -241,13 +241,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
             int buf = 0;
             uint32_t p_par = 0;
-#ifdef DECA_FA_PROFILE
-            long long m_kv = 0, m_pa = 0, m_pb = 0, m_issue = 0, m_t0 = clock64();
-#endif
             for (int j = 0; j < n_b && ok; ++j) {
-#ifdef DECA_FA_PROFILE
-                long long c0 = clock64();
-#endif
                 const int jn = j + NSB;  // tile whose scores are issued in this step (its K is at kp)
                 // V_j and K_jn (if any) must have landed
                 if (!mbar_wait(kv_full(vp.slot), vp.par, abort_flag)) {
@@ -259,10 +253,6 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     ok = false;
                 }
                 if (!ok) break;
-#ifdef DECA_FA_PROFILE
-                long long c1 = clock64();
-                m_kv += c1 - c0;
-#endif
                 // group A: once P_A(j) is ready its score buffer is consumed as well
                 if (j < n_a) {
                     if (!mbar_wait(p_full(0, buf), p_par, abort_flag)) {
@@ -271,11 +261,6 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         break;
                     }
                     tc_fence_after_sync();
-#ifdef DECA_FA_PROFILE
-                    long long c2 = clock64();
-                    m_pa += c2 - c1;
-                    c1 = c2;
-#endif
                     if constexpr (PTMEM) {
                         // the product reads P from the buffer the next score MMA overwrites
                         issue_pv(0, buf, vp, (uint32_t)j);
@@ -285,10 +270,6 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         issue_pv(0, buf, vp, (uint32_t)j);
                     }
                 }
-#ifdef DECA_FA_PROFILE
-                long long c3 = clock64();
-                m_issue += c3 - c1;
-#endif
                 // group B (always the last user of K_jn and V_j)
                 if (!mbar_wait(p_full(1, buf), p_par, abort_flag)) {
                     report_detail(g.status, 1, 6, j);
@@ -296,10 +277,6 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     break;
                 }
                 tc_fence_after_sync();
-#ifdef DECA_FA_PROFILE
-                long long c4 = clock64();
-                m_pb += c4 - c3;
-#endif
                 if constexpr (PTMEM) {
                     issue_pv(1, buf, vp, (uint32_t)j);
                     umma_commit(kv_empty(vp.slot));
@@ -318,18 +295,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 advance2(vp);
                 if (jn < n_b) advance2(kp);
                 if (++buf == NSB) buf = 0, p_par ^= 1u;
-#ifdef DECA_FA_PROFILE
-                m_issue += clock64() - c4;
-#endif
             }
-#ifdef DECA_FA_PROFILE
-            if (blockIdx.x == 0 && blockIdx.y == 0) {
-                g.status->detail[0] = (unsigned)(m_kv / n_b);
-                g.status->detail[1] = (unsigned)(m_pa / n_b);
-                g.status->detail[2] = (unsigned)(m_pb / n_b);
-                g.status->detail[3] = (unsigned)(m_issue / n_b);
-            }
-#endif
             if (!ok) {
                 if (*abort_flag == 0) {
                     *abort_flag = 1;
@@ -359,25 +325,14 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag)) != 0;
         };
 
-#ifdef DECA_FA_PROFILE
-        long long t_wait = 0, t_step = 0, t_sig = 0, t_all = clock64();
-        long long g_fa_prof[4] = {0, 0, 0, 0};
-#endif
         for (int j = 0; j < n_kv; ++j) {
             const int buf = j % NSB;
-#ifdef DECA_FA_PROFILE
-            long long c0 = clock64();
-#endif
             if (!wait_all(s_full(grp, buf), (uint32_t)((j / NSB) & 1))) {
                 if (lane == 0 && q == 0) report_detail(g.status, 2 + grp, 7, j);
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-#ifdef DECA_FA_PROFILE
-            long long c1 = clock64();
-            t_wait += c1 - c0;
-#endif
             const uint32_t tSg = tS(grp, buf) + lane_off;
             const uint32_t pb = PTMEM ? tSg : sP + grp * kPBytes;
             const bool diag = g.causal && ((j + 1) * kBc - 1 > qt * kBr);
@@ -391,37 +346,20 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             // P in tensor memory reuses the score buffer that was just filled: free by construction
             auto wait_p = [&]() { return PTMEM || wait_prev(); };
             const bool step_ok = diag ? fa_softmax_step<kBc, D, true, PTMEM>(tSg, tOg, pb, r, col0, row_abs, sl2, j == 0,
-                                                                             m, l, wait_p, wait_prev DECA_FA_PROF_ARG)
+                                                                             m, l, wait_p, wait_prev)
                                       : fa_softmax_step<kBc, D, false, PTMEM>(tSg, tOg, pb, r, col0, row_abs, sl2, j == 0,
-                                                                              m, l, wait_p, wait_prev DECA_FA_PROF_ARG);
+                                                                              m, l, wait_p, wait_prev);
             if (!step_ok) {
                 if (lane == 0 && q == 0) report_detail(g.status, 2 + grp, 8, j);
                 ok = false;
                 break;
             }
-#ifdef DECA_FA_PROFILE
-            long long c2 = clock64();
-            t_step += c2 - c1;
-#endif
             // S is consumed, P (and a possibly rescaled O) are ready
             fence_proxy_async_smem();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full(grp, buf));
-#ifdef DECA_FA_PROFILE
-            t_sig += clock64() - c2;
-#endif
         }
-#ifdef DECA_FA_PROFILE
-        if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && q == 0) {
-            g.status->detail[4 + grp * 4 + 0] = (unsigned)(t_wait / n_kv);
-            g.status->detail[4 + grp * 4 + 1] = (unsigned)(t_step / n_kv);
-            g.status->detail[4 + grp * 4 + 2] = (unsigned)(t_sig / n_kv);
-            g.status->detail[4 + grp * 4 + 3] = (unsigned)((clock64() - t_all) / n_kv);
-            if (grp == 1 && g_fa_prof[3] > 0)  // first load, exponential pass, P store
-                for (int i = 0; i < 3; ++i) g.status->detail[8 + i] = (unsigned)(g_fa_prof[i] / g_fa_prof[3]);
-        }
-#endif
 
         if (ok) {
             ok = wait_all(pv_done(grp, (n_kv - 1) % NSB), (uint32_t)(((n_kv - 1) / NSB) & 1));

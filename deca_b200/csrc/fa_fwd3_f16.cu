@@ -331,9 +331,6 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const float sl2 = g.sl2;
         bool ok = true;
         uint32_t cnt = 0;  // tiles of this group handled so far (all items)
-#ifdef DECA_FA_PROFILE
-        long long g_fa_prof[4] = {0, 0, 0, 0};  // counters are only reported by the one-item-per-CTA kernel
-#endif
         auto wait_all = [&](uint32_t bar, uint32_t parity) {
             return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag)) != 0;
         };
@@ -363,9 +360,9 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 auto wait_p = [&]() { return true; };  // P reuses the score tile that was just filled
                 const bool step_ok =
                     diag ? fa_softmax_step<kBc, D, true, true>(tSg, tOg, tSg, r, col0, row_abs, sl2, j == 0, m, l, wait_p,
-                                                               wait_prev DECA_FA_PROF_ARG)
+                                                               wait_prev)
                          : fa_softmax_step<kBc, D, false, true>(tSg, tOg, tSg, r, col0, row_abs, sl2, j == 0, m, l, wait_p,
-                                                                wait_prev DECA_FA_PROF_ARG);
+                                                                wait_prev);
                 if (!step_ok) {
                     if (lane == 0 && q == 0) report_detail(g.status, 2 + grp, 8, j);
                     ok = false;

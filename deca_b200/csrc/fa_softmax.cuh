@@ -18,15 +18,6 @@
 
 namespace deca {
 
-#ifdef DECA_FA_PROFILE
-// cycle counters of the instrumented build (per thread): first tensor-memory load, the whole
-// exponential pass (including that load), the P store, number of fast-path tiles
-#define DECA_FA_PROF_PARAM , long long (&g_fa_prof)[4]
-#define DECA_FA_PROF_ARG , g_fa_prof
-#else
-#define DECA_FA_PROF_PARAM
-#define DECA_FA_PROF_ARG
-#endif
 
 constexpr float kFaRescaleThreshold = 8.0f;  // log2 units
 constexpr float kFaSumLimit = 256.0f;        // 2^threshold: bound of a tile's row sum on the fast path
@@ -119,19 +110,13 @@ __device__ __forceinline__ void fa_exp_chunk32(const uint32_t (&v)[32], int cb0,
 // The tensor-memory load of the next 32 columns is in flight while the current 32 are processed.
 template <int BC, bool MASKED>
 __device__ __forceinline__ float fa_exp_tile_hold(uint32_t tS, int col0, int row_abs, float sl2, float ms,
-                                                  uint32_t (&pk)[BC / 2] DECA_FA_PROF_PARAM) {
+                                                  uint32_t (&pk)[BC / 2]) {
     constexpr int kChunks = BC / 32;
     const uint64_t sl2x2 = f32x2_pack(sl2, sl2), nmsx2 = f32x2_pack(-ms, -ms);
     uint64_t sum2[2] = {0ull, 0ull};
     uint32_t v[2][32];
-#ifdef DECA_FA_PROFILE
-    const long long pc0 = clock64();
-#endif
     tmem_ld_32x32b_x32(tS, v[0]);
     tmem_ld_wait_regs(v[0]);
-#ifdef DECA_FA_PROFILE
-    g_fa_prof[0] += clock64() - pc0;
-#endif
 #pragma unroll
     for (int c = 0; c < kChunks; ++c) {
         if (c + 1 < kChunks) tmem_ld_32x32b_x32(tS + (c + 1) * 32, v[(c + 1) & 1]);
@@ -140,9 +125,6 @@ __device__ __forceinline__ float fa_exp_tile_hold(uint32_t tS, int col0, int row
                                &pk[(c / 2) * 32 + (c % 2) * 16]);
         if (c + 1 < kChunks) tmem_ld_wait_regs(v[(c + 1) & 1]);
     }
-#ifdef DECA_FA_PROFILE
-    g_fa_prof[1] += clock64() - pc0;
-#endif
     float a0, a1, b0, b1;
     f32x2_unpack(sum2[0], a0, a1);
     f32x2_unpack(sum2[1], b0, b1);
@@ -180,7 +162,7 @@ __device__ __forceinline__ float fa_row_max(uint32_t tS, int col0, int row_abs) 
 template <int BC, int D, bool MASKED, bool PTMEM, typename WaitP, typename WaitO>
 __device__ __forceinline__ bool fa_softmax_step(uint32_t tS, uint32_t tO, uint32_t p_base, int r, int col0, int row_abs,
                                                 float sl2, bool first_tile, float &m, float &l, WaitP wait_p_free,
-                                                WaitO wait_o_ready DECA_FA_PROF_PARAM) {
+                                                WaitO wait_o_ready) {
     if (!wait_p_free()) return false;
     float mx, lsum = 0.f;
     bool have_p = false, raise;
@@ -212,11 +194,8 @@ __device__ __forceinline__ bool fa_softmax_step(uint32_t tS, uint32_t tO, uint32
         // (no score grew by more than the threshold) without a max over the scores; a larger sum
         // sends the warp down the slow path, where the exact maximum is taken and m raised.
         uint32_t pk[BC / 2];
-        lsum = fa_exp_tile_hold<BC, MASKED>(tS, col0, row_abs, sl2, m * sl2, pk DECA_FA_PROF_ARG);
+        lsum = fa_exp_tile_hold<BC, MASKED>(tS, col0, row_abs, sl2, m * sl2, pk);
         const bool slow = __any_sync(0xFFFFFFFFu, !(lsum <= kFaSumLimit)) != 0;
-#ifdef DECA_FA_PROFILE
-        const long long pc1 = clock64();
-#endif
         if (!slow) {
 #pragma unroll
             for (int h = 0; h < BC / 64; ++h) {
@@ -226,10 +205,6 @@ __device__ __forceinline__ bool fa_softmax_step(uint32_t tS, uint32_t tO, uint32
                 tmem_st_32x32b_x32(p_base + h * 32, part);
             }
             tmem_st_wait();
-#ifdef DECA_FA_PROFILE
-            g_fa_prof[2] += clock64() - pc1;
-            g_fa_prof[3] += 1;
-#endif
             l += lsum;
             return true;
         }

@@ -111,6 +111,9 @@ struct RowArgs {
     int tpr;  // threads per row
     float eps;
     float inv_n;
+    // optional [M, 2] fp32 output of the row statistics as the kernel computed them (null: off):
+    // softmax (row max * log2 e, 1 / sum of exponentials); RMSNorm (rsqrt(mean x^2 + eps), sum x^2)
+    float *stats;
 };
 
 // ------------------------------------------------------------------------------------------
@@ -174,6 +177,7 @@ __global__ void rowwise_reg_kernel(const RowArgs a) {
             }
         s = row_reduce<SumOp>(s, red[1], nw, row_warp0, wr, lane);
         const float inv = 1.0f / s;
+        if (a.stats != nullptr && t == 0) a.stats[2 * row] = ml, a.stats[2 * row + 1] = inv;
 #pragma unroll
         for (int c = 0; c < C; ++c) {
             const int col = (c * tpr + t) * VEC;
@@ -204,6 +208,7 @@ __global__ void rowwise_reg_kernel(const RowArgs a) {
             }
         ss = row_reduce<SumOp>(ss, red[0], nw, row_warp0, wr, lane);
         const float r = rsqrtf(ss * a.inv_n + a.eps);
+        if (a.stats != nullptr && t == 0) a.stats[2 * row] = r, a.stats[2 * row + 1] = ss;
 #pragma unroll
         for (int c = 0; c < C; ++c) {
             const int col = (c * tpr + t) * VEC;
@@ -321,8 +326,9 @@ __global__ void rowwise_twopass_kernel(const RowArgs a) {
     } else {
         const float ss = row_reduce<SumOp>(s_run, red[0], nw, row_warp0, wr, lane);
         scale0 = rsqrtf(ss * a.inv_n + a.eps);
-        scale1 = 0.f;
+        scale1 = ss;
     }
+    if (a.stats != nullptr && t == 0) a.stats[2 * row] = scale0, a.stats[2 * row + 1] = scale1;
 
     // pass 2
     auto emit = [&](const uint32_t(&xin)[WORDS], int col) {
@@ -517,8 +523,10 @@ extern "C" int deca_rowwise_default_config(int op, int dtype, int64_t M, int64_t
     return deca_rowwise_check_config(op, dtype, M, N, out);
 }
 
-extern "C" int deca_rowwise(int op, int dtype, const void *X, const void *W, void *Y, int64_t M, int64_t N,
-                            float eps, const deca_row_cfg *cfg, void *stream) {
+namespace {
+
+int rowwise_impl(int op, int dtype, const void *X, const void *W, void *Y, float *stats, int64_t M, int64_t N, float eps,
+                 const deca_row_cfg *cfg, void *stream) {
     if (!X || !Y || (op == DECA_RMSNORM && !W)) return DECA_ERR_NULL;
     deca_row_cfg c;
     int rc;
@@ -529,8 +537,10 @@ extern "C" int deca_rowwise(int op, int dtype, const void *X, const void *W, voi
         rc = deca_rowwise_default_config(op, dtype, M, N, &c);
     }
     if (rc != DECA_OK) return rc;
-    if (c.mode == DECA_ROW_TMA)
+    if (c.mode == DECA_ROW_TMA) {
+        if (stats) return DECA_ERR_UNSUPPORTED;  // the bulk-copy mode has no statistics output
         return rowwise_tma_launch(op, dtype, X, W, Y, M, N, eps, c, static_cast<cudaStream_t>(stream));
+    }
     const size_t al = (size_t)c.vec * 2;
     if (!aligned_to(X, al) || !aligned_to(Y, al) || (op == DECA_RMSNORM && !aligned_to(W, al))) return DECA_ERR_ALIGN;
 
@@ -543,6 +553,7 @@ extern "C" int deca_rowwise(int op, int dtype, const void *X, const void *W, voi
     a.tpr = c.threads_per_row;
     a.eps = eps;
     a.inv_n = 1.0f / (float)N;
+    a.stats = stats;
     const unsigned grid = (unsigned)(M / c.rows_per_block);
     const unsigned threads = (unsigned)(c.threads_per_row * c.rows_per_block);
     const int64_t span = (int64_t)c.threads_per_row * c.vec;
@@ -554,4 +565,18 @@ extern "C" int deca_rowwise(int op, int dtype, const void *X, const void *W, voi
                                  : launch_vec<DECA_SOFTMAX, DECA_BF16>(c, chunks, a, grid, threads, st);
     return dtype == DECA_F16 ? launch_vec<DECA_RMSNORM, DECA_F16>(c, chunks, a, grid, threads, st)
                              : launch_vec<DECA_RMSNORM, DECA_BF16>(c, chunks, a, grid, threads, st);
+}
+
+}  // namespace
+
+extern "C" int deca_rowwise(int op, int dtype, const void *X, const void *W, void *Y, int64_t M, int64_t N,
+                            float eps, const deca_row_cfg *cfg, void *stream) {
+    return rowwise_impl(op, dtype, X, W, Y, nullptr, M, N, eps, cfg, stream);
+}
+
+extern "C" int deca_rowwise_stats(int op, int dtype, const void *X, const void *W, void *Y, float *stats, int64_t M,
+                                  int64_t N, float eps, const deca_row_cfg *cfg, void *stream) {
+    if (!stats) return DECA_ERR_NULL;
+    if (!aligned_to(stats, 8)) return DECA_ERR_ALIGN;
+    return rowwise_impl(op, dtype, X, W, Y, stats, M, N, eps, cfg, stream);
 }

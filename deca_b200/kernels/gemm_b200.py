@@ -33,6 +33,7 @@ class GemmConfig:
     cta_group: int = 1  # 2: two CTAs of a cluster share one 256-row MMA tile
     acc_bufs: int = 2  # tensor-memory accumulator buffers
     stream_k: bool = False  # cut the k blocks of the last tiles into one equal share per SM
+    acc_f16: bool = False  # fp16 accumulators (tcgen05 D type f16) instead of fp32: fp16 inputs, one-CTA tiles only
 
     @property
     def threads(self) -> int:
@@ -46,6 +47,7 @@ class GemmConfig:
             f"{self.BM}x{self.BN}x{self.BK},cta={self.cta_group},stages={self.stages},"
             f"raster={self.raster},epi_smem={int(self.epi_smem)},acc={self.acc_bufs}"
             + (",sk=1" if self.stream_k else "")
+            + (",acc_f16=1" if self.acc_f16 else "")
         )
 
 
@@ -78,6 +80,8 @@ def check_config(cfg: GemmConfig, M: int, N: int, K: int, max_smem: int = MAX_DY
     if cfg.cta_group == 2:
         # CTA pairs: a (2 BM) x BN tile, each CTA holds BM rows and fetches half of the B columns
         assert cfg.BN in (128, 256) and cfg.epi_smem and not cfg.stream_k
+    if cfg.acc_f16:  # fp16 accumulators: one-CTA kernel, whole tiles (split tiles exchange fp32 partial sums)
+        assert cfg.cta_group == 1 and not cfg.stream_k
     assert 2 <= cfg.stages <= 8
     assert cfg.raster >= 1
     assert tmem_columns(cfg) <= TMEM_COLUMNS
@@ -87,40 +91,25 @@ def check_config(cfg: GemmConfig, M: int, N: int, K: int, max_smem: int = MAX_DY
     assert N % 8 == 0 and K % 8 == 0
 
 
-def default_config(M: int, N: int, K: int) -> GemmConfig:
-    """A reasonable config without tuning.  Large problems take the 256 x 256 tile (one B tile
-    feeds two MMAs, which halves the L2 -> shared-memory traffic per flop; measured 1.40 PFLOPS
-    at 4096^3 against 1.28 for 128 x 256); smaller ones shrink the tile until every SM has one."""
-    sms = 148
+def default_config(M: int, N: int, K: int, acc_f16: bool = False, sms: int = 148) -> GemmConfig:
+    """The config the native library uses when none is given (``deca_gemm16_default_config``, a
+    host-only call): 256 x 256 tiles once they give every SM one (one B tile feeds two MMAs, which
+    halves the L2 -> shared-memory traffic per flop), else the best-scoring narrower tile."""
+    import ctypes
 
-    def tiles(bm, bn):
-        return -(-M // bm) * -(-N // bn)
+    from .. import native
 
-    if tiles(256, 256) >= sms:
-        bm, bn, stages, acc = 256, 256, 3, 1
-    else:
-        # fewer tiles than SMs: weigh the share of SMs a tile shape keeps busy against the rate of
-        # its main loop (narrower tiles re-read A from shared memory more often per flop)
-        cands = [((128, 256, 4, 2), 1.0), ((128, 128, 6, 2), 0.8), ((128, 64, 8, 2), 0.55)]
-        def score(c):
-            (bm_, bn_, _, _), rate = c
-            if bn_ > max(64, 2 * N):
-                return 0.0
-            t = tiles(bm_, bn_)
-            useful = M * N / (t * bm_ * bn_)  # partial tiles compute zero-filled rows / columns
-            return rate * useful * t / (-(-t // sms) * sms)
-        (bm, bn, stages, acc), _ = max(cands, key=score)
-    stages = max(2, min(stages, -(-K // 64)))  # no deeper than the number of K blocks
-    gm = -(-M // bm)
-    raster = 8
-    while raster > 1 and gm < raster:
-        raster //= 2
-    return GemmConfig(BM=bm, BN=bn, stages=stages, raster=raster, acc_bufs=acc)
+    c = native.GemmCfg()
+    native.check(native.lib().deca_gemm16_default_config(M, N, K, sms, int(acc_f16), ctypes.byref(c)),
+                 "deca_gemm16_default_config")
+    return GemmConfig(BM=c.BM, BN=c.BN, BK=c.BK, stages=c.stages, raster=c.raster, epi_smem=bool(c.epi_smem),
+                      cta_group=c.cta_group, acc_bufs=c.acc_bufs, stream_k=bool(c.stream_k), acc_f16=bool(c.acc_f16))
 
 
 def make_gemm_tc(M: int, N: int, K: int, cfg: GemmConfig, dtype: str = "float16") -> KernelSpec:
     check_config(cfg, M, N, K)
     assert dtype in GEMM_DTYPES
+    assert not cfg.acc_f16 or dtype == "float16", "fp16 accumulation needs fp16 inputs"
     return KernelSpec("gemm", (M, N, K), dtype, cfg.as_dict())
 
 
@@ -138,7 +127,7 @@ def native_cfg(cfg: GemmConfig):
     from .. import native
 
     return native.GemmCfg(cfg.BM, cfg.BN, cfg.BK, cfg.stages, cfg.raster, int(cfg.epi_smem), cfg.cta_group,
-                          cfg.acc_bufs, int(cfg.stream_k))
+                          cfg.acc_bufs, int(cfg.stream_k), int(cfg.acc_f16))
 
 
 def stream_k_plan(cfg: GemmConfig, M: int, N: int, K: int, sms: int = 148):

@@ -41,7 +41,7 @@ class RowCfg(ctypes.Structure):
 
 class GemmCfg(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in ("BM", "BN", "BK", "stages", "raster", "epi_smem", "cta_group", "acc_bufs",
-                                            "stream_k")]
+                                            "stream_k", "acc_f16")]
 
 
 class FaCfg(ctypes.Structure):
@@ -63,10 +63,12 @@ def lib() -> ctypes.CDLL:
         L.deca_status_string.argtypes = [ctypes.c_int]
         vp, i64, ci, cf = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
         L.deca_rowwise.argtypes = [ci, ci, vp, vp, vp, i64, i64, cf, ctypes.POINTER(RowCfg), vp]
+        L.deca_rowwise_stats.argtypes = [ci, ci, vp, vp, vp, vp, i64, i64, cf, ctypes.POINTER(RowCfg), vp]
         L.deca_rowwise_check_config.argtypes = [ci, ci, i64, i64, ctypes.POINTER(RowCfg)]
         L.deca_rowwise_default_config.argtypes = [ci, ci, i64, i64, ctypes.POINTER(RowCfg)]
         L.deca_gemm16_check_config.argtypes = [ci, i64, i64, i64, ctypes.POINTER(GemmCfg)]
         L.deca_gemm16.argtypes = [ci, vp, vp, vp, i64, i64, i64, ctypes.POINTER(GemmCfg), vp]
+        L.deca_gemm16_default_config.argtypes = [i64, i64, i64, ci, ci, ctypes.POINTER(GemmCfg)]
         L.deca_gemm16_workspace_bytes.argtypes = [ci, i64, i64, i64, ctypes.POINTER(GemmCfg), ctypes.POINTER(ctypes.c_size_t)]
         L.deca_gemm16_ws.argtypes = [ci, vp, vp, vp, i64, i64, i64, ctypes.POINTER(GemmCfg), vp, ctypes.c_size_t, vp]
         L.deca_gemm16_sk_static.argtypes = [ci, vp, vp, vp, i64, i64, i64, ctypes.POINTER(GemmCfg), vp]

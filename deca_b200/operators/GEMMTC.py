@@ -1,10 +1,11 @@
 """16-bit tensor-core GEMM operator (C = A @ B, fp32 accumulation, 16-bit output).
 
-Same record as the reference's src/operators/GEMMTC.py:19-111.  ``acc="fp16"`` (and
-``acc_splits``) are accepted for call-site compatibility and keep the reference's looser
-tolerance for that mode, but the kernel is the same: the tcgen05 path accumulates in fp32
-tensor memory at full rate, so there is nothing to gain from an fp16 accumulator and the
-result is the more accurate one.  ``dtype`` may also be "bfloat16".
+Same record as the reference's src/operators/GEMMTC.py:19-111.  ``acc="fp16"`` selects fp16
+accumulators (``GemmConfig.acc_f16``: the accumulator type of tcgen05.mma set to f16, every
+16-deep partial sum rounded to fp16, the reference's looser tolerance for that mode);
+``acc_splits`` is accepted and recorded (it enters the tolerance and ``describe()`` as in the
+reference) but the tensor-memory accumulator is a single one.  ``dtype`` may also be
+"bfloat16" (fp32 accumulation only).
 """
 
 import math
@@ -21,6 +22,7 @@ class GEMMTC(Operator):
                  name: str = "GEMMTC"):
         assert dtype in ("float16", "bfloat16"), "GEMMTC only supports float16 / bfloat16 inputs"
         assert acc in ("fp32", "fp16")
+        assert acc == "fp32" or dtype == "float16", "fp16 accumulation needs float16 inputs"
         self.M, self.N, self.K = M, N, K
         self.dtype = dtype
         self.acc = acc
@@ -44,6 +46,8 @@ class GEMMTC(Operator):
         return (1e-2 * math.sqrt(self.K / 1024), 2e-3)
 
     def is_valid(self, cfg: GemmConfig) -> bool:
+        if cfg.acc_f16 != (self.acc == "fp16"):  # as the reference does (GEMMTC.py:65-67)
+            return False
         try:
             check_config(cfg, self.M, self.N, self.K)
             return True
@@ -61,7 +65,7 @@ class GEMMTC(Operator):
     def default_config(self) -> GemmConfig:
         from ..kernels.gemm_b200 import default_config
 
-        return default_config(self.M, self.N, self.K)
+        return default_config(self.M, self.N, self.K, acc_f16=self.acc == "fp16")
 
     def __call__(self, a, b, out=None, cfg: GemmConfig | None = None):
         """Runs the kernel: returns C = A @ B."""

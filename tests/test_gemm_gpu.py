@@ -302,3 +302,67 @@ def test_cta_pair_config_rules(native):
     assert rc(256, 256, 64, 3, 8, 1, 2, 2, 0) == -4  # one accumulator (all 512 columns)
     assert rc(256, 256, 64, 3, 8, 1, 2, 1, 1) == -4  # no stream-K
     assert rc(256, 256, 64, 3, 8, 1, 3, 1, 0) == -4
+
+
+# ---------------------------------------------------------------------------- fp16 accumulation
+@pytest.mark.parametrize("shape,tile", [((640, 768, 448), (128, 256, 4, 2)), ((1280, 1024, 1024), (256, 256, 3, 1)),
+                                        ((300, 520, 4096), (128, 128, 6, 2)), ((256, 256, 16), (128, 64, 2, 2))],
+                         ids=lambda v: "x".join(map(str, v)))
+def test_fp16_accumulate_mode(native, shape, tile):
+    """``acc_f16``: the tensor cores accumulate in fp16 (the reference's ``acc_f16`` configs,
+    gemm_tir.py:52-58).  Bound: the reference's tolerance for that mode against the fp32 result,
+    atol = 2e-3 * K, rtol = 1e-2 (operators/GEMMTC.py:60-62).  The mode must be a real one: with a
+    deep K its results differ from the fp32-accumulating kernel's and are less accurate, while one
+    16-deep step (a single MMA per output) is accumulated exactly and rounds the same way."""
+    M, N, K = shape
+    BM, BN, stages, acc = tile
+    a_bits, b_bits = make_ab(M, N, K, "float16", seed=12)
+    a, b = bits_to_torch(a_bits, "float16"), bits_to_torch(b_bits, "float16")
+    out = {}
+    for f16 in (0, 1):
+        buf = torch.full((M + 2, N), 7.0, dtype=torch.float16, device="cuda")
+        ccfg = native.GemmCfg(BM, BN, 64, min(stages, max(2, -(-K // 64))), 2, 1, 1, acc, 0, f16)
+        rc = native.lib().deca_gemm16(native.F16, a.data_ptr(), b.data_ptr(), buf[1 : M + 1].data_ptr(), M, N, K,
+                                      ctypes.byref(ccfg), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert rc == 0, native.status_string(rc)
+        assert native.last_device_status() == (0, 0, 0)
+        assert torch.all(buf[0] == 7.0) and torch.all(buf[M + 1] == 7.0), "canary rows overwritten"
+        out[f16] = oracle.from_bits(torch_to_bits(buf[1 : M + 1]), "float16")
+    _, c32 = oracle.gemm16(a_bits, b_bits, "float16", want_f32=True)
+    err32, err16 = np.abs(out[0] - c32), np.abs(out[1] - c32)
+    assert np.all(err16 <= 2e-3 * K + 1e-2 * np.abs(c32)), f"max err {err16.max()}"
+    if K == 16:
+        assert np.array_equal(out[0], out[1]), "a single MMA per output is accumulated exactly"
+    else:
+        assert err16.max() > err32.max() and np.mean(out[0] != out[1]) > 0.05, "the mode changed nothing"
+        # each of the K / 16 partial sums is rounded to fp16 once: a random walk of half-ulp steps
+        assert err16.max() <= 8.0 * math.sqrt(K / 16) * 2.0**-11 * max(1.0, np.abs(c32).max())
+
+
+def test_fp16_accumulate_operator_and_rules(native):
+    from deca_b200.kernels.gemm_b200 import GemmConfig
+    from deca_b200.operators import GEMMTC
+
+    M, N, K = 512, 512, 2048
+    g = torch.Generator(device="cpu").manual_seed(3)
+    a = (torch.rand(M, K, generator=g) * 2 - 1).half().cuda()
+    b = (torch.rand(K, N, generator=g) * 2 - 1).half().cuda()
+    op = GEMMTC(M, N, K, acc="fp16", acc_splits=1)
+    assert op.describe() == "GEMMTC(M=512, N=512, K=2048, float16, acc=fp16x1)"
+    c = op(a, b)
+    torch.cuda.synchronize()
+    ref = op.reference((a, b))
+    atol, rtol = op.tolerance
+    assert torch.all((c.float() - ref).abs() <= atol + rtol * ref.abs())
+    assert not torch.equal(c, GEMMTC(M, N, K)(a, b))
+    L = native.lib()
+    rc = lambda dt, cfg: L.deca_gemm16_check_config(dt, M, N, K, ctypes.byref(cfg))  # noqa: E731
+    assert rc(native.F16, native.GemmCfg(128, 256, 64, 4, 8, 1, 1, 2, 0, 1)) == 0
+    assert rc(native.BF16, native.GemmCfg(128, 256, 64, 4, 8, 1, 1, 2, 0, 1)) == -4   # fp16 inputs only
+    assert rc(native.F16, native.GemmCfg(128, 256, 64, 4, 8, 1, 2, 2, 0, 1)) == -4    # not on CTA pairs
+    assert rc(native.F16, native.GemmCfg(128, 256, 64, 4, 8, 1, 1, 2, 1, 1)) == -4    # not with stream-K
+    assert rc(native.F16, native.GemmCfg(128, 256, 64, 4, 8, 1, 1, 2, 0, 2)) == -4
+    with pytest.raises(AssertionError):
+        GEMMTC(M, N, K, dtype="bfloat16", acc="fp16")
+    assert not op.is_valid(GemmConfig()) and op.is_valid(GemmConfig(acc_f16=True))

@@ -214,3 +214,92 @@ def test_argument_errors(native):
     bad = native.RowCfg(32, 3, 8, 0, 1, 0)  # rows_per_block does not divide M
     assert L.deca_rowwise(0, 0, x.data_ptr(), None, y.data_ptr(), 8, 64, f, ctypes.byref(bad), st) == -4
     torch.cuda.synchronize()
+
+
+# ------------------------------------------------------------------ row statistics (fp32 path)
+def run_native_stats(native, op, dtype, x_bits, w_bits, cfg=None, eps=1e-6):
+    """deca_rowwise_stats: the outputs plus the two fp32 statistics per row the kernel reduced to."""
+    M, N = x_bits.shape
+    x = bits_to_torch(x_bits, dtype)
+    w = bits_to_torch(w_bits, dtype) if w_bits is not None else None
+    y = torch.empty_like(x)
+    stats = torch.full((M, 2), float("nan"), dtype=torch.float32, device="cuda")
+    ccfg = None
+    if cfg is not None:
+        ccfg = ctypes.byref(native.RowCfg(cfg["tpr"], cfg.get("rpb", 1), cfg.get("vec", 8),
+                                          native.ROW_MODE_CODE[cfg.get("mode", "reg")], cfg.get("unroll", 1),
+                                          int(cfg.get("hint", False))))
+    st = native.lib().deca_rowwise_stats(
+        native.ROW_OP_CODE[op], native.DTYPE_CODE[dtype], x.data_ptr(), w.data_ptr() if w is not None else None,
+        y.data_ptr(), stats.data_ptr(), M, N, ctypes.c_float(eps), ccfg,
+        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert st == 0, native.status_string(st)
+    return torch_to_bits(y), stats.cpu().numpy()
+
+
+STATS_CONFIGS = [None, dict(tpr=64, rpb=2), dict(tpr=256, mode="twopass", unroll=2), dict(tpr=128, vec=4, hint=True)]
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("cfg", STATS_CONFIGS, ids=lambda c: "default" if c is None else ",".join(f"{k}={v}" for k, v in c.items()))
+def test_rmsnorm_fp32_statistic_and_exact_rounding(native, dtype, cfg):
+    """The only fp32 quantity of RMSNorm is r = rsqrt(mean(x^2) + eps): it must match an exact
+    (float64) computation to 1e-3 relative -- it does to 5e-6 -- and, given the kernel's own r, EVERY
+    output bit must follow from the reference's rounding sequence dt(f32(dt(x * r)) * w)
+    (rowwise_tir.py:340-350).  This is the 1e-3 bound without any 16-bit rounding term."""
+    eps = 1e-6
+    for shape, scale in (((512, 4096), 3.0), ((34, 1000), 0.01), ((8, 16384), 40.0)):
+        x_bits, w_bits = make_x(*shape, dtype, seed=13, scale=scale)
+        y_bits, stats = run_native_stats(native, "rmsnorm", dtype, x_bits, w_bits, cfg, eps)
+        assert np.array_equal(y_bits, run_native(native, "rmsnorm", dtype, x_bits, w_bits, cfg, eps)), "same kernel, same bits"
+        x32, w32 = oracle.from_bits(x_bits, dtype), oracle.from_bits(w_bits, dtype)
+        x64 = x32.astype(np.float64)
+        r_exact = 1.0 / np.sqrt((x64 * x64).mean(axis=1) + eps)
+        r = stats[:, 0]
+        assert np.all(np.abs(r - r_exact) <= 5e-6 * r_exact), f"rsqrt off by {(np.abs(r - r_exact) / r_exact).max():.2e}"
+        assert np.all(np.abs(stats[:, 1] - (x64 * x64).sum(axis=1)) <= 5e-6 * (x64 * x64).sum(axis=1))
+        normed = oracle.from_bits(oracle.to_bits(x32 * r[:, None].astype(np.float32), dtype), dtype)
+        want_bits = oracle.to_bits(normed * w32[None, :], dtype)
+        assert np.array_equal(y_bits, want_bits), f"{np.mean(y_bits != want_bits):.2e} of the outputs differ"
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("cfg", STATS_CONFIGS, ids=lambda c: "default" if c is None else ",".join(f"{k}={v}" for k, v in c.items()))
+def test_softmax_fp32_statistics_and_rounding(native, dtype, cfg):
+    """Softmax reduces a row to (max * log2 e, 1 / sum of exponentials): the first is exact, the second
+    must match a float64 computation to 1e-3 relative (it does to 1e-5); given them, every output is
+    the correctly rounded 16-bit value of exp2(x * log2 e - max * log2 e) / sum up to the 2^-22
+    accuracy of the hardware exponential (rowwise_tir.py:279-300)."""
+    for shape, scale in (((512, 4096), 3.0), ((34, 1000), 0.3), ((4, 32000), 6.0)):
+        if cfg is not None and cfg.get("mode", "reg") == "reg" and shape[1] > 32 * cfg["tpr"] * cfg.get("vec", 8):
+            continue  # the row does not fit this config's registers
+        x_bits, _ = make_x(*shape, dtype, seed=17, scale=scale)
+        y_bits, stats = run_native_stats(native, "softmax", dtype, x_bits, None, cfg)
+        assert np.array_equal(y_bits, run_native(native, "softmax", dtype, x_bits, None, cfg))
+        x32 = oracle.from_bits(x_bits, dtype)
+        log2e = np.float32(1.4426950408889634)
+        ml = x32.max(axis=1) * log2e
+        assert np.array_equal(stats[:, 0], ml), "row max * log2(e) is an exact fp32 product"
+        x64 = x32.astype(np.float64)
+        s_exact = np.exp2(x64 * float(log2e) - ml.astype(np.float64)[:, None]).sum(axis=1)
+        inv = stats[:, 1].astype(np.float64)
+        assert np.all(np.abs(inv * s_exact - 1.0) <= 1e-5), f"1/sum off by {np.abs(inv * s_exact - 1).max():.2e}"
+        arg = (x32 * log2e - ml[:, None]).astype(np.float64)  # fma in the kernel: within half an fp32 ulp of this
+        y_exact = np.exp2(arg) * inv[:, None]
+        got = oracle.from_bits(y_bits, dtype).astype(np.float64)
+        # half a 16-bit ulp of rounding + the fp32 error of the exponential and of its argument
+        slack = 0.5 * ulp(y_exact, dtype) * 1.0001 + 1e-5 * y_exact + (3e-8 if dtype == "float16" else 0.0)
+        assert np.all(np.abs(got - y_exact) <= slack), f"max excess x{(np.abs(got - y_exact) / slack).max():.3f}"
+
+
+def test_stats_argument_errors(native):
+    L = native.lib()
+    x = torch.zeros(8, 1024, dtype=torch.float16, device="cuda")
+    st = ctypes.c_void_p(0)
+    eps = ctypes.c_float(1e-6)
+    assert L.deca_rowwise_stats(0, 0, x.data_ptr(), None, x.data_ptr(), None, 8, 1024, eps, None, st) == -1
+    stats = torch.zeros(8, 2, device="cuda")
+    tma = native.RowCfg(128, 2, 8, native.ROW_TMA, 2, 0)
+    assert L.deca_rowwise_stats(0, 0, x.data_ptr(), None, x.data_ptr(), stats.data_ptr(), 8, 1024, eps, ctypes.byref(tma), st) == -5
+    torch.cuda.synchronize()

@@ -32,8 +32,19 @@ def test_every_gemm_solution_is_valid_and_ranked(arch):
     # large squares: the model's favourite is the tile shape measured best on B200
     best = rank_gemm_configs(solve_gemm_tc(arch, 8192, 8192, 8192), arch, 8192, 8192, 8192)[0]
     assert (best.BM, best.BN) == (256, 256)
-    # fp16-accumulate call sites get the same (fp32-accumulating) configs
-    assert set(solve_gemm_tc(arch, 4096, 4096, 4096, acc_f16=True, acc_splits=2)) == set(solve_gemm_tc(arch, 4096, 4096, 4096))
+    # fp16-accumulate call sites get the one-CTA, whole-tile part of the same tile space with fp16 accumulators
+    from dataclasses import replace
+
+    from deca_b200.operators import GEMMTC
+
+    f16 = solve_gemm_tc(arch, 4096, 4096, 4096, acc_f16=True, acc_splits=2)
+    f32 = [c for c in solve_gemm_tc(arch, 4096, 4096, 4096) if c.cta_group == 1 and not c.stream_k]
+    assert f16 and all(c.acc_f16 for c in f16)
+    assert {replace(c, acc_f16=False) for c in f16} == set(f32)
+    op16, op32 = GEMMTC(4096, 4096, 4096, acc="fp16", acc_splits=2), GEMMTC(4096, 4096, 4096)
+    assert op16.is_valid(f16[0]) and not op16.is_valid(f32[0]) and not op32.is_valid(f16[0])
+    assert op16.default_config().acc_f16 and not op32.default_config().acc_f16
+    assert str(f16[0]).endswith(",acc_f16=1") and "acc_f16" not in str(f32[0])
 
 
 def test_every_attention_solution_is_valid(arch):
