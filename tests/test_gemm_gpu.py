@@ -313,7 +313,7 @@ def test_fp16_accumulate_mode(native, shape, tile):
     gemm_tir.py:52-58).  Bound: the reference's tolerance for that mode against the fp32 result,
     atol = 2e-3 * K, rtol = 1e-2 (operators/GEMMTC.py:60-62).  The mode must be a real one: with a
     deep K its results differ from the fp32-accumulating kernel's and are less accurate, while one
-    16-deep step (a single MMA per output) is accumulated exactly and rounds the same way."""
+    16-deep step (a single MMA per output) gives the same sum up to the last bit of its rounding."""
     M, N, K = shape
     BM, BN, stages, acc = tile
     a_bits, b_bits = make_ab(M, N, K, "float16", seed=12)
@@ -333,7 +333,10 @@ def test_fp16_accumulate_mode(native, shape, tile):
     err32, err16 = np.abs(out[0] - c32), np.abs(out[1] - c32)
     assert np.all(err16 <= 2e-3 * K + 1e-2 * np.abs(c32)), f"max err {err16.max()}"
     if K == 16:
-        assert np.array_equal(out[0], out[1]), "a single MMA per output is accumulated exactly"
+        # one 16-deep step per output: the same sum, rounded to fp16 by the tensor core instead of by
+        # the epilogue (the two roundings may differ in the last bit)
+        assert np.all(np.abs(out[0] - out[1]) <= 2.0 ** (np.floor(np.log2(np.maximum(np.abs(c32), 2.0**-14))) - 10))
+        assert np.mean(out[0] == out[1]) > 0.9
     else:
         assert err16.max() > err32.max() and np.mean(out[0] != out[1]) > 0.05, "the mode changed nothing"
         # each of the K / 16 partial sums is rounded to fp16 once: a random walk of half-ulp steps
