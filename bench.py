@@ -56,6 +56,10 @@ NCU_TRAFFIC_BYTES = {
     # GEMM 4096^3: 80.51 MB read + 6.59 MB written (C mostly still in L2)
     "gemm_f16_4096x4096x4096": 87099392,
 }
+# Traffic of shapes captured at another batch or row count, where it grows in proportion:
+# attention B2 H16 S4096 D128: 100.82 MB + 11.12 MB (non-causal), 100.82 MB + 15.53 MB (causal); x 2 for B = 4
+NCU_TRAFFIC_BYTES["fa_fwd_f16_4x16x4096x128"] = 2 * (100822016 + 11123712)
+NCU_TRAFFIC_BYTES["fa_fwd_f16_4x16x4096x128_causal"] = 2 * (100815104 + 15534080)
 
 
 def measured_peaks():
@@ -274,7 +278,7 @@ class GemmWorkload(Workload):
 
         a, b, c = self.sets[0]
         self.host = (a.cpu().pin_memory(), b.cpu().pin_memory(), torch.empty(self.M, self.N, dtype=torch.float16).pin_memory())
-        self.e2e_rows = max(256, self.M // 8)
+        self.e2e_rows = max(256, self.M // 16)  # 16 chunks: the last chunk's kernel and copy-out are the pipeline's tail
         self.e2e_op = GEMMTC(self.e2e_rows, self.N, self.K)
         self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
 

@@ -61,16 +61,22 @@ def solve_gemm_tc(arch, M: int, N: int, K: int, type_size: int = 2, count: int =
     results = []
     gm_of = {128: -(-M // 128), 256: -(-M // 256)}
     for vals in _all_models(s, (bm, bn, st, epi, acc), count):
-        for ras in (1, 2, 4, 8, 16):
-            if ras > 1 and ras > gm_of[vals[0]]:
-                continue
+        gn = -(-N // vals[1])
+        # tile order: groups of `ras` tile rows walked along N, or (tall problems) of `ras` tile columns
+        # walked down M, which keeps a band of the smaller operand B in L2
+        orders = [(ras, False) for ras in (1, 2, 4, 8, 16) if ras == 1 or ras <= gm_of[vals[0]]]
+        if M > N:
+            orders += [(ras, True) for ras in (2, 4, 8, 16) if ras <= gn]
+        for ras, along_n in orders:
             cfg = GemmConfig(BM=vals[0], BN=vals[1], BK=64, stages=vals[2], raster=ras, epi_smem=bool(vals[3]),
-                             cta_group=1, acc_bufs=vals[4], acc_f16=acc_f16)
+                             cta_group=1, acc_bufs=vals[4], acc_f16=acc_f16, raster_n=along_n)
             try:
                 check_config(cfg, M, N, K)
             except AssertionError:
                 continue
             results.append(cfg)
+            if along_n:
+                continue
             # the stream-K form of the config, where whole tiles would leave a quarter of a wave idle
             tiles = gm_of[vals[0]] * -(-N // vals[1])
             sms = arch.sm_nums

@@ -33,12 +33,14 @@ def gemm_wave_dram_bytes_per_flop(cfg, arch: Arch, M: int, N: int, K: int, slots
     output in groups of ``raster`` tile rows; operands that fit in half the L2 are fetched once."""
     if (M * K + K * N) * 2 <= 0.5 * arch.l2_bytes:
         return (M * K + K * N) * 2 / (2.0 * M * N * K)
-    GM, GN = -(-M // cfg.BM), -(-N // cfg.BN)
+    GM, GN, BM, BN = -(-M // cfg.BM), -(-N // cfg.BN), cfg.BM, cfg.BN
+    if getattr(cfg, "raster_n", False):  # groups of tile columns walked down M: the roles of M and N swap
+        GM, GN, BM, BN = GN, GM, BN, BM
     g = max(1, min(cfg.raster, GM))
     cols = min(GN, math.ceil(slots / g))
     rows = min(GM, g * math.ceil(slots / (g * GN)))
     tiles = min(slots, GM * GN)
-    return (rows * cfg.BM + cols * cfg.BN) / (tiles * cfg.BM * cfg.BN)
+    return (rows * BM + cols * BN) / (tiles * BM * BN)
 
 
 def gemm_tc_score(cfg, arch: Arch, M: int, N: int, K: int) -> float:

@@ -33,6 +33,7 @@ class GemmConfig:
     cta_group: int = 1  # 2: two CTAs of a cluster share one 256-row MMA tile
     acc_bufs: int = 2  # tensor-memory accumulator buffers
     stream_k: bool = False  # cut the k blocks of the last tiles into one equal share per SM
+    raster_n: bool = False  # raster groups are tile columns walked down M (keeps a band of B in L2; for M > N)
     acc_f16: bool = False  # fp16 accumulators (tcgen05 D type f16) instead of fp32: fp16 inputs, one-CTA tiles only
 
     @property
@@ -47,6 +48,7 @@ class GemmConfig:
             f"{self.BM}x{self.BN}x{self.BK},cta={self.cta_group},stages={self.stages},"
             f"raster={self.raster},epi_smem={int(self.epi_smem)},acc={self.acc_bufs}"
             + (",sk=1" if self.stream_k else "")
+            + (",raster_n=1" if self.raster_n else "")
             + (",acc_f16=1" if self.acc_f16 else "")
         )
 
@@ -80,6 +82,8 @@ def check_config(cfg: GemmConfig, M: int, N: int, K: int, max_smem: int = MAX_DY
     if cfg.cta_group == 2:
         # CTA pairs: a (2 BM) x BN tile, each CTA holds BM rows and fetches half of the B columns
         assert cfg.BN in (128, 256) and cfg.epi_smem and not cfg.stream_k
+    if cfg.raster_n:
+        assert cfg.cta_group == 1
     if cfg.acc_f16:  # fp16 accumulators: one-CTA kernel, whole tiles (split tiles exchange fp32 partial sums)
         assert cfg.cta_group == 1 and not cfg.stream_k
     assert 2 <= cfg.stages <= 8
@@ -103,7 +107,8 @@ def default_config(M: int, N: int, K: int, acc_f16: bool = False, sms: int = 148
     native.check(native.lib().deca_gemm16_default_config(M, N, K, sms, int(acc_f16), ctypes.byref(c)),
                  "deca_gemm16_default_config")
     return GemmConfig(BM=c.BM, BN=c.BN, BK=c.BK, stages=c.stages, raster=c.raster, epi_smem=bool(c.epi_smem),
-                      cta_group=c.cta_group, acc_bufs=c.acc_bufs, stream_k=bool(c.stream_k), acc_f16=bool(c.acc_f16))
+                      cta_group=c.cta_group, acc_bufs=c.acc_bufs, stream_k=bool(c.stream_k), raster_n=bool(c.raster_n),
+                      acc_f16=bool(c.acc_f16))
 
 
 def make_gemm_tc(M: int, N: int, K: int, cfg: GemmConfig, dtype: str = "float16") -> KernelSpec:
@@ -127,7 +132,7 @@ def native_cfg(cfg: GemmConfig):
     from .. import native
 
     return native.GemmCfg(cfg.BM, cfg.BN, cfg.BK, cfg.stages, cfg.raster, int(cfg.epi_smem), cfg.cta_group,
-                          cfg.acc_bufs, int(cfg.stream_k), int(cfg.acc_f16))
+                          cfg.acc_bufs, int(cfg.stream_k), int(cfg.acc_f16), int(cfg.raster_n))
 
 
 def stream_k_plan(cfg: GemmConfig, M: int, N: int, K: int, sms: int = 148):

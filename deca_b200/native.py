@@ -41,7 +41,7 @@ class RowCfg(ctypes.Structure):
 
 class GemmCfg(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in ("BM", "BN", "BK", "stages", "raster", "epi_smem", "cta_group", "acc_bufs",
-                                            "stream_k", "acc_f16")]
+                                            "stream_k", "acc_f16", "raster_n")]
 
 
 class FaCfg(ctypes.Structure):

@@ -369,3 +369,34 @@ def test_fp16_accumulate_operator_and_rules(native):
     with pytest.raises(AssertionError):
         GEMMTC(M, N, K, dtype="bfloat16", acc="fp16")
     assert not op.is_valid(GemmConfig()) and op.is_valid(GemmConfig(acc_f16=True))
+
+
+@pytest.mark.parametrize("shape,tile", [((2304, 640, 192), (128, 128, 3, 2)), ((4096, 1024, 256), (256, 256, 3, 1)),
+                                        ((1000, 520, 136), (128, 64, 2, 2)), ((8192, 768, 128), (128, 256, 2, 2))],
+                         ids=lambda v: "x".join(map(str, v)))
+def test_column_band_tile_order(native, shape, tile):
+    """``raster_n``: the tiles are walked in groups of tile columns down M instead of tile rows along
+    N.  Only the order changes, so every output bit equals the row-group order's, for group widths
+    that divide the tile grid, do not divide it, and exceed it."""
+    M, N, K = shape
+    BM, BN, stages, acc = tile
+    a_bits, b_bits = make_ab(M, N, K, "float16", seed=15)
+    a, b = bits_to_torch(a_bits, "float16"), bits_to_torch(b_bits, "float16")
+
+    def run(raster, along_n):
+        buf = torch.full((M + 2, N), 7.0, dtype=torch.float16, device="cuda")
+        ccfg = native.GemmCfg(BM, BN, 64, stages, raster, 1, 1, acc, raster_n=along_n)
+        rc = native.lib().deca_gemm16(native.F16, a.data_ptr(), b.data_ptr(), buf[1 : M + 1].data_ptr(), M, N, K,
+                                      ctypes.byref(ccfg), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert rc == 0, native.status_string(rc)
+        assert native.last_device_status() == (0, 0, 0)
+        assert torch.all(buf[0] == 7.0) and torch.all(buf[M + 1] == 7.0), "canary rows overwritten"
+        return torch_to_bits(buf[1 : M + 1])
+
+    want = run(4, 0)
+    check("float16", a_bits, b_bits, want)
+    for raster in (1, 2, 3, 8, 64):
+        assert np.array_equal(run(raster, 1), want), f"raster={raster}"
+    pair = native.GemmCfg(128, 256, 64, 4, 4, 1, 2, 2, raster_n=1)
+    assert native.lib().deca_gemm16_check_config(native.F16, M, N, K, ctypes.byref(pair)) == -4

@@ -161,3 +161,45 @@ def test_gemm_default_config_and_stream_k_plan():
         check_config(GemmConfig(BM=256, BN=256, stages=3, acc_bufs=2, cta_group=2), 4096, 4096, 4096)
     with pytest.raises(AssertionError):
         check_config(GemmConfig(BM=128, BN=64, stages=4, acc_bufs=2, cta_group=2), 4096, 4096, 4096)
+
+
+def test_reference_import_roots_and_root_clis():
+    """The reference's scripts put <root>/src and <root> on sys.path (test_gemm_tc.py:23-24) and import
+    ``operators``, ``kernels.*_tir``, ``Solver``, ``RuntimeMod``, ``cost_model.CostModel``,
+    ``src.utils.helper`` and ``arch.*``: the same statements must resolve here, to the very classes of
+    the ``deca_b200`` package, and the three command lines must exist at the repository root."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = f"""
+import os, sys
+sys.path[:0] = [os.path.join({root!r}, "src"), {root!r}]
+from operators import GEMMTC, RMSNorm, Softmax
+from operators.FlashAttention import FlashAttention
+from kernels.gemm_tir import GemmConfig, build_gemm_tc_to_file, check_config
+from kernels.flash_attn_tir import FAConfig, build_flash_attn_to_file
+from kernels.rowwise_tir import RowConfig, build_rowwise_to_file
+from kernels.attn_bench import bench_interleaved, make_qkv, sdpa_flash, standard_shapes
+from kernels.gemm_bench import torch_ref
+from kernels.rowwise_bench import rowwise_bytes
+from Solver import solve_flash_attn, solve_gemm_tc, solve_rowwise
+from cost_model.CostModel import rank_fa_configs, rank_gemm_configs, rank_rowwise_configs
+from RuntimeMod import RuntimeMod
+from src.utils.helper import GPUDetector
+from arch.B200 import B200
+import deca_b200.operators as ops, deca_b200.RuntimeMod as rm, deca_b200.utils.helper as helper
+assert GEMMTC is ops.GEMMTC and FlashAttention is ops.FlashAttention and Softmax is ops.Softmax
+assert RuntimeMod is rm.RuntimeMod and GPUDetector is helper.GPUDetector
+assert "NVIDIA B200" in GPUDetector.GPU_MODEL_MAP
+rt = RuntimeMod(FlashAttention(1, 1, 128, 128, 64), B200(), True, FAConfig())
+assert rt.is_flash_attn
+cfgs = solve_rowwise(B200(), "softmax", 16384, 4096)
+assert rank_rowwise_configs(cfgs, B200(), "softmax", 16384, 4096)[0] in cfgs
+print("ok")
+"""
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd="/tmp")
+    assert res.returncode == 0 and res.stdout.strip().endswith("ok"), res.stderr[-2000:]
+    for cli in ("test_gemm_tc.py", "test_flash_attn.py", "test_rowwise.py"):
+        res = subprocess.run([sys.executable, os.path.join(root, cli), "--help"], capture_output=True, text=True, cwd="/tmp")
+        assert res.returncode == 0 and "--shape" in res.stdout and "--sweep" in res.stdout, res.stderr[-500:]
