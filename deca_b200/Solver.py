@@ -150,7 +150,9 @@ def solve_rowwise(arch, op: str, M: int, N: int, type_size: int = 2, twopass_min
 
     Modes: 0 = reg (row in registers), 1 = twopass (row streamed twice), 2 = tma (persistent
     CTAs, rows through shared-memory rings with bulk copies).  As in the reference, twopass is
-    only offered for rows of at least ``twopass_min_n`` elements unless nothing else fits.
+    only offered for rows of at least ``twopass_min_n`` elements unless nothing else fits.  Rows of
+    that length also get the cluster mode (a thread-block cluster of 2, 4 or 8 CTAs per row, each
+    caching a slice in registers: one pass where twopass needs two), enumerated directly.
     """
     from .kernels.rowwise_b200 import RowConfig, check_config
 
@@ -190,4 +192,16 @@ def solve_rowwise(arch, op: str, M: int, N: int, type_size: int = 2, twopass_min
         (fallback if (cfg.mode == "twopass" and only_short) else results).append(cfg)
     if not results:
         results = fallback
-    return results[:count]
+    results = results[:count]
+    if N >= twopass_min_n:
+        for cs in (2, 4, 8):
+            for threads in (256, 512, 1024):
+                for v in ((8, 4) if N % 8 == 0 else (4,) if N % 4 == 0 else (2,)):
+                    for h in (False, True):
+                        cfg = RowConfig(threads_per_row=threads, rows_per_block=1, vec=v, mode="cluster", unroll=cs, hint=h)
+                        try:
+                            check_config(cfg, op, M, N, "float16")
+                        except AssertionError:
+                            continue
+                        results.append(cfg)
+    return results

@@ -237,9 +237,10 @@ def rowwise_score(cfg, arch: Arch, op: str, M: int, N: int, type_size: int = 2) 
         in_flight = cfg.rows_per_block * cfg.unroll * N * type_size
         phase = 1.0
     else:
-        per_thread = (chunks if cfg.mode == "reg" else cfg.unroll) * cfg.vec * type_size
+        cached = cfg.mode in ("reg", "cluster")  # the whole row (slice) is requested up front
+        per_thread = (chunks if cached else cfg.unroll) * cfg.vec * type_size
         in_flight = ctas * cfg.threads * per_thread
-        phase = 1.0 - 0.35 / ctas if cfg.mode == "reg" else 1.0 - 0.1 / ctas
+        phase = 1.0 - 0.35 / ctas if cached else 1.0 - 0.1 / ctas
     mem = min(1.0, in_flight / need)
 
     # instruction issue: elements per clock per SM needed at full bandwidth vs what the resident
@@ -254,7 +255,7 @@ def rowwise_score(cfg, arch: Arch, op: str, M: int, N: int, type_size: int = 2) 
         grid_eff = 1.0
         coupling = 0.9  # per-row barrier round trips of the single persistent CTA (measured)
     else:
-        grid = M // cfg.rows_per_block
+        grid = M // cfg.rows_per_block * (cfg.unroll if cfg.mode == "cluster" else 1)
         slots = arch.sm_nums * ctas
         grid_eff = grid / (math.ceil(grid / slots) * slots)
         coupling = 0.88 ** math.log2(cfg.rows_per_block) if cfg.threads > 128 else 1.0
@@ -267,7 +268,10 @@ def rowwise_score(cfg, arch: Arch, op: str, M: int, N: int, type_size: int = 2) 
 
     nw = cfg.threads_per_row // 32
     reduce = 1.0 / (1.0 + 0.02 * math.log2(nw or 1) + (0.03 if nw > 1 else 0.0))
-    tail = N / (chunks * cfg.threads_per_row * cfg.vec) if cfg.mode != "twopass" else 1.0
+    if cfg.mode == "cluster":  # a cluster barrier per reduction on top of the CTA's own
+        reduce /= 1.0 + 0.02 * math.log2(cfg.unroll)
+    covered = chunks * cfg.threads_per_row * cfg.vec * (cfg.unroll if cfg.mode == "cluster" else 1)
+    tail = N / covered if cfg.mode != "twopass" else 1.0
     lanes = 1.0 if cfg.vec * type_size >= 16 else 0.97
     hint = 1.01 if cfg.hint else 1.0
     return mem * phase * issue * grid_eff * coupling * reduce * (0.7 + 0.3 * tail) * lanes * hint / passes

@@ -13,6 +13,11 @@
 //   twopass : rows too long for registers: pass 1 keeps an online (max, sum) / a sum of
 //             squares per thread, pass 2 re-reads the row (from L2 when the rows in flight
 //             fit) and writes the result.
+//   cluster : rows too long for the registers of ONE CTA stay one-pass: a thread-block cluster
+//             of 2, 4 or 8 CTAs shares a row, each CTA caches its contiguous slice in registers
+//             as in reg mode, and the row statistics are combined across the cluster through
+//             distributed shared memory (every CTA stores its partial value into each peer's
+//             slot, one cluster barrier per reduction).  No second pass, no clusters across GPUs.
 //
 // Softmax keeps exp2(x*log2e - max*log2e) of the cached row in fp32 registers between the
 // sum and the output pass, so the MUFU unit sees each element once, and takes the row
@@ -101,6 +106,9 @@ __device__ __forceinline__ float row_reduce(float v, float *red, int nw, int row
     }
     return v;
 }
+
+// Elements of a row each CTA of a `cs`-CTA cluster takes: an equal share rounded up to whole vectors.
+inline int cluster_slice(int N, int cs, int vec) { return ((N + cs - 1) / cs + vec - 1) / vec * vec; }
 
 struct RowArgs {
     const char *x;
@@ -219,6 +227,148 @@ __global__ void rowwise_reg_kernel(const RowArgs a) {
                 for (int i = 0; i < WORDS; ++i) {
                     float2 f = P::unpack(cache[c][i]);
                     // x * r is rounded to the I/O dtype before the weight multiply
+                    float2 n = P::unpack(P::pack(f.x * r, f.y * r));
+                    float2 g = P::unpack(wv[i]);
+                    o[i] = P::pack(n.x * g.x, n.y * g.y);
+                }
+                store_words<WORDS, HINT>(yrow + (size_t)col * 2, o);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Cluster mode: one row per cluster, one contiguous slice of it per CTA, cached in registers.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t row_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void row_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Every CTA of the cluster holds `v` (its slice's value) in all threads; returns the combination
+// over the cluster.  `slots` is this CTA's array of one float per cluster rank: thread i < cs
+// stores v into slot [my rank] of CTA i, the cluster barrier publishes the stores.
+template <typename Op>
+__device__ __forceinline__ float cluster_combine(float v, float *slots, uint32_t rank, uint32_t cs) {
+    if (threadIdx.x < cs) {
+        const uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(slots + rank));
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(threadIdx.x));
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+    }
+    row_cluster_sync();
+    float r = slots[0];
+    for (uint32_t i = 1; i < cs; ++i) r = Op::apply(r, slots[i]);
+    return r;
+}
+
+template <int OP, int DT, int WORDS, int C, bool HINT>
+__global__ void rowwise_cluster_kernel(const RowArgs a, int cs, int slice) {
+    using P = Pack16<DT>;
+    constexpr int VEC = 2 * WORDS;
+    __shared__ float red[2][32];
+    __shared__ float cl[2][8];
+
+    const int tpr = blockDim.x;  // the whole CTA works on one slice
+    const int t = threadIdx.x;
+    const int lane = t & 31;
+    const int wr = t >> 5;
+    const int nw = tpr >> 5;
+    const uint32_t rank = row_cluster_rank();
+    const long long row = blockIdx.x / cs;
+    const int s0 = (int)rank * slice;              // first element of this CTA's slice
+    const int s1 = min(a.N, s0 + slice);           // one past its last
+    const char *xrow = a.x + row * a.N * 2;
+    char *yrow = a.y + row * a.N * 2;
+
+    uint32_t cache[C][WORDS];
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int col = s0 + (c * tpr + t) * VEC;
+        if (col < s1) {
+            load_words<WORDS, HINT>(cache[c], xrow + (size_t)col * 2);
+        } else {
+#pragma unroll
+            for (int i = 0; i < WORDS; ++i) cache[c][i] = (OP == DECA_SOFTMAX) ? P::kNegInfPair : 0u;
+        }
+    }
+
+    // every CTA of the cluster must be running before a peer stores into its shared memory; the
+    // loads above are already in flight while this barrier completes
+    row_cluster_sync();
+
+    if constexpr (OP == DECA_SOFTMAX) {
+        uint32_t mx = cache[0][0];
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+#pragma unroll
+            for (int i = 0; i < WORDS; ++i) mx = P::max2(mx, cache[c][i]);
+        float2 mf = P::unpack(mx);
+        float m = row_reduce<MaxOp>(fmaxf(mf.x, mf.y), red[0], nw, 0, wr, lane);
+        m = cluster_combine<MaxOp>(m, cl[0], rank, (uint32_t)cs);
+        const float ml = m * kLog2e;
+
+        constexpr bool KEEP_E = (C * VEC <= 128);
+        float e[KEEP_E ? C : 1][VEC];
+        float s = 0.f;
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+#pragma unroll
+            for (int i = 0; i < WORDS; ++i) {
+                float2 f = P::unpack(cache[c][i]);
+                const float e0 = ex2_approx(fmaf(f.x, kLog2e, -ml));
+                const float e1 = ex2_approx(fmaf(f.y, kLog2e, -ml));
+                if constexpr (KEEP_E) e[c][2 * i] = e0, e[c][2 * i + 1] = e1;
+                s += e0 + e1;
+            }
+        s = row_reduce<SumOp>(s, red[1], nw, 0, wr, lane);
+        s = cluster_combine<SumOp>(s, cl[1], rank, (uint32_t)cs);
+        const float inv = 1.0f / s;
+        if (a.stats != nullptr && t == 0 && rank == 0) a.stats[2 * row] = ml, a.stats[2 * row + 1] = inv;
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            const int col = s0 + (c * tpr + t) * VEC;
+            if (col < s1) {
+                uint32_t o[WORDS];
+#pragma unroll
+                for (int i = 0; i < WORDS; ++i) {
+                    if constexpr (KEEP_E) {
+                        o[i] = P::pack(e[c][2 * i] * inv, e[c][2 * i + 1] * inv);
+                    } else {
+                        float2 f = P::unpack(cache[c][i]);
+                        o[i] = P::pack(ex2_approx(fmaf(f.x, kLog2e, -ml)) * inv,
+                                       ex2_approx(fmaf(f.y, kLog2e, -ml)) * inv);
+                    }
+                }
+                store_words<WORDS, HINT>(yrow + (size_t)col * 2, o);
+            }
+        }
+    } else {
+        float ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+#pragma unroll
+            for (int i = 0; i < WORDS; ++i) {
+                float2 f = P::unpack(cache[c][i]);
+                ss = fmaf(f.x, f.x, ss);
+                ss = fmaf(f.y, f.y, ss);
+            }
+        ss = row_reduce<SumOp>(ss, red[0], nw, 0, wr, lane);
+        ss = cluster_combine<SumOp>(ss, cl[0], rank, (uint32_t)cs);
+        const float r = rsqrtf(ss * a.inv_n + a.eps);
+        if (a.stats != nullptr && t == 0 && rank == 0) a.stats[2 * row] = r, a.stats[2 * row + 1] = ss;
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            const int col = s0 + (c * tpr + t) * VEC;
+            if (col < s1) {
+                uint32_t wv[WORDS], o[WORDS];
+                load_words<WORDS, false>(wv, a.w + (size_t)col * 2);
+#pragma unroll
+                for (int i = 0; i < WORDS; ++i) {
+                    float2 f = P::unpack(cache[c][i]);
                     float2 n = P::unpack(P::pack(f.x * r, f.y * r));
                     float2 g = P::unpack(wv[i]);
                     o[i] = P::pack(n.x * g.x, n.y * g.y);
@@ -428,10 +578,41 @@ int launch_twopass(int unroll, const RowArgs &a, unsigned grid, unsigned threads
     return DECA_ERR_CONFIG;
 }
 
+// Cluster mode: `grid` clusters of `cs` CTAs, one row each; the slice of a CTA is `slice` elements.
+template <int OP, int DT, int WORDS, int C, bool HINT>
+int launch_cluster_c(const RowArgs &a, unsigned rows, unsigned threads, int cs, int slice, cudaStream_t st) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows * (unsigned)cs), cfg.blockDim = dim3(threads), cfg.dynamicSmemBytes = 0, cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = (unsigned)cs, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr, cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, rowwise_cluster_kernel<OP, DT, WORDS, C, HINT>, a, cs, slice);
+}
+
+template <int OP, int DT, int WORDS, bool HINT>
+int launch_cluster(int chunks, const RowArgs &a, unsigned rows, unsigned threads, int cs, int slice, cudaStream_t st) {
+#define DECA_CL_CASE(CN) \
+    if (chunks <= CN) return launch_cluster_c<OP, DT, WORDS, CN, HINT>(a, rows, threads, cs, slice, st);
+    DECA_CL_CASE(1)
+    DECA_CL_CASE(2)
+    DECA_CL_CASE(3)
+    DECA_CL_CASE(4)
+    DECA_CL_CASE(6)
+    DECA_CL_CASE(8)
+#undef DECA_CL_CASE
+    return DECA_ERR_CONFIG;
+}
+
 template <int OP, int DT, int WORDS, bool HINT>
 int launch_mode(const deca_row_cfg &c, int chunks, const RowArgs &a, unsigned grid, unsigned threads,
                 cudaStream_t st) {
     if (c.mode == DECA_ROW_REG) return launch_reg<OP, DT, WORDS, HINT>(chunks, a, grid, threads, st);
+    if (c.mode == DECA_ROW_CLUSTER) {
+        const int slice = cluster_slice(a.N, c.unroll, c.vec);
+        const int span = c.threads_per_row * c.vec;
+        return launch_cluster<OP, DT, WORDS, HINT>((slice + span - 1) / span, a, (unsigned)a.M, threads, c.unroll, slice, st);
+    }
     return launch_twopass<OP, DT, WORDS, HINT>(c.unroll, a, grid, threads, st);
 }
 
@@ -465,6 +646,24 @@ extern "C" int deca_rowwise_check_config(int op, int dtype, int64_t M, int64_t N
     if (dtype != DECA_F16 && dtype != DECA_BF16) return DECA_ERR_UNSUPPORTED;
     if (M <= 0 || N <= 0 || N > (1ll << 30)) return DECA_ERR_SHAPE;
     if (cfg->mode == DECA_ROW_TMA) return rowwise_tma_check(op, M, N, *cfg);
+    if (cfg->mode == DECA_ROW_CLUSTER) {
+        // a cluster of `unroll` CTAs (2, 4 or 8) of `threads_per_row` threads per row; a CTA caches its
+        // slice of the row in registers (at most 8 chunks per thread)
+        if (cfg->vec != 8 && cfg->vec != 4 && cfg->vec != 2) return DECA_ERR_CONFIG;
+        if (N % cfg->vec != 0) return DECA_ERR_CONFIG;
+        if (cfg->unroll != 2 && cfg->unroll != 4 && cfg->unroll != 8) return DECA_ERR_CONFIG;
+        if (cfg->rows_per_block != 1) return DECA_ERR_CONFIG;
+        if (cfg->threads_per_row < 32 || cfg->threads_per_row % 32 != 0 || cfg->threads_per_row > 1024) return DECA_ERR_CONFIG;
+        if (M * cfg->unroll > 2147483647ll) return DECA_ERR_SHAPE;
+        const int64_t slice = cluster_slice((int)N, cfg->unroll, cfg->vec);
+        const int64_t span = (int64_t)cfg->threads_per_row * cfg->vec;
+        const int64_t chunks = (slice + span - 1) / span;
+        if (chunks > 8) return DECA_ERR_CONFIG;
+        const int64_t elems = chunks * cfg->vec;
+        const int64_t regs = (op == DECA_SOFTMAX ? (elems <= 128 ? elems : elems / 2 + cfg->vec) : elems / 2 + cfg->vec) + 28;
+        if (regs > 255 || regs * cfg->threads_per_row > 65536) return DECA_ERR_CONFIG;
+        return DECA_OK;
+    }
     if (cfg->mode != DECA_ROW_REG && cfg->mode != DECA_ROW_TWOPASS) return DECA_ERR_CONFIG;
     if (cfg->vec != 8 && cfg->vec != 4 && cfg->vec != 2) return DECA_ERR_CONFIG;
     if (N % cfg->vec != 0) return DECA_ERR_CONFIG;
@@ -554,7 +753,7 @@ int rowwise_impl(int op, int dtype, const void *X, const void *W, void *Y, float
     a.eps = eps;
     a.inv_n = 1.0f / (float)N;
     a.stats = stats;
-    const unsigned grid = (unsigned)(M / c.rows_per_block);
+    const unsigned grid = (unsigned)(M / (c.rows_per_block > 0 ? c.rows_per_block : 1));
     const unsigned threads = (unsigned)(c.threads_per_row * c.rows_per_block);
     const int64_t span = (int64_t)c.threads_per_row * c.vec;
     const int chunks = (int)((N + span - 1) / span);

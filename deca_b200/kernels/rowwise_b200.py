@@ -16,7 +16,8 @@ LOG2E = 1.4426950408889634
 NEG_INF = -1e30
 OPS = ("softmax", "rmsnorm")
 DTYPES = ("float16", "bfloat16")
-MODES = ("reg", "twopass", "tma")
+MODES = ("reg", "twopass", "tma", "cluster")
+MAX_CLUSTER_CHUNKS = 8  # chunk counts the cluster-mode kernels are instantiated for
 MAX_REGS_PER_SM = 65536
 MAX_REG_CHUNKS = 32  # chunk counts the register-mode kernels are instantiated for
 MAX_TMA_CHUNKS = 16
@@ -32,7 +33,8 @@ class RowConfig:
     rows_per_block: int = 1
     vec: int = 8  # elements per vector access (8 -> 16 B for 16-bit dtypes)
     mode: str = "reg"
-    # twopass: chunks loaded back to back per iteration; tma: rows in flight per row group
+    # twopass: chunks loaded back to back per iteration; tma: rows in flight per row group;
+    # cluster: CTAs of the thread-block cluster that shares a row (2, 4 or 8)
     unroll: int = 1
     hint: bool = False  # no-allocate loads and streaming stores
 
@@ -45,11 +47,18 @@ class RowConfig:
 
     def __str__(self):
         s = f"tpr={self.threads_per_row},rpb={self.rows_per_block},vec={self.vec},mode={self.mode}"
-        s += f",unroll={self.unroll}" if self.mode in ("twopass", "tma") else ""
+        s += f",unroll={self.unroll}" if self.mode in ("twopass", "tma", "cluster") else ""
         return s + (",hint=1" if self.hint else "")
 
 
+def cluster_slice(cfg: RowConfig, N: int) -> int:
+    """Elements of a row one CTA of the cluster takes: an equal share rounded up to whole vectors."""
+    return -(-(-(-N // cfg.unroll)) // cfg.vec) * cfg.vec
+
+
 def num_chunks(cfg: RowConfig, N: int) -> int:
+    if cfg.mode == "cluster":
+        N = cluster_slice(cfg, N)
     return -(-N // (cfg.threads_per_row * cfg.vec))
 
 
@@ -60,7 +69,7 @@ def est_regs_per_thread(cfg: RowConfig, N: int, op: str) -> int:
     keeps the exponentials in fp32 up to KEEP_EXP_ELEMS elements (one register each, the packed
     copy dies as they are produced); RMSNorm keeps only the packed row plus one weight chunk.
     """
-    if cfg.mode in ("reg", "tma"):
+    if cfg.mode in ("reg", "tma", "cluster"):
         elems = num_chunks(cfg, N) * cfg.vec
         if op == "softmax":
             regs = (elems if elems <= KEEP_EXP_ELEMS else elems // 2 + cfg.vec) + 24
@@ -92,6 +101,14 @@ def check_config(cfg: RowConfig, op: str, M: int, N: int, dtype: str) -> None:
         assert tma_smem_bytes(cfg, op, N) <= MAX_DYN_SMEM
         return
     assert cfg.vec in (2, 4, 8) and N % cfg.vec == 0
+    if cfg.mode == "cluster":
+        # one row per cluster of `unroll` CTAs; each CTA caches its slice of the row in registers
+        assert cfg.unroll in (2, 4, 8) and cfg.rows_per_block == 1
+        assert cfg.threads_per_row % 32 == 0 and 32 <= cfg.threads_per_row <= 1024
+        assert num_chunks(cfg, N) <= MAX_CLUSTER_CHUNKS
+        regs = est_regs_per_thread(cfg, N, op) + 4
+        assert regs <= 255 and regs * cfg.threads <= MAX_REGS_PER_SM
+        return
     assert cfg.threads_per_row % 32 == 0 and cfg.threads_per_row >= 32 and cfg.threads <= 1024
     assert cfg.rows_per_block >= 1 and M % cfg.rows_per_block == 0
     assert cfg.unroll in (1, 2, 4)

@@ -15,10 +15,10 @@ _lib = None
 
 F16, BF16 = 0, 1
 SOFTMAX, RMSNORM = 0, 1
-ROW_REG, ROW_TWOPASS, ROW_TMA = 0, 1, 2
+ROW_REG, ROW_TWOPASS, ROW_TMA, ROW_CLUSTER = 0, 1, 2, 3
 DTYPE_CODE = {"float16": F16, "bfloat16": BF16}
 ROW_OP_CODE = {"softmax": SOFTMAX, "rmsnorm": RMSNORM}
-ROW_MODE_CODE = {"reg": ROW_REG, "twopass": ROW_TWOPASS, "tma": ROW_TMA}
+ROW_MODE_CODE = {"reg": ROW_REG, "twopass": ROW_TWOPASS, "tma": ROW_TMA, "cluster": ROW_CLUSTER}
 ROW_MODE_NAME = {v: k for k, v in ROW_MODE_CODE.items()}
 
 

@@ -1,8 +1,11 @@
-"""Row-wise memory-bound operators over an [M, N] input (reduction over N).
+"""Row-wise memory-bound operators over an [M, N] input (reduction over N): the base record and
+its two operators.
 
-Same record as the reference's src/operators/Rowwise.py:23-73: a ``RowConfig`` fully
-determines the kernel; the operator provides the inputs, the torch reference and the
-tolerance RuntimeMod verifies against.  Calling the operator runs the kernel.
+Same records as the reference's src/operators/Rowwise.py:23-73, Softmax.py:8-18 and
+RMSNorm.py:9-22: a ``RowConfig`` fully determines the kernel; the operator provides the inputs,
+the torch reference and the tolerance RuntimeMod verifies against.  Calling the operator runs the
+kernel.  ``Softmax(M, N, dtype)``: y = softmax(x, -1).  ``RMSNorm(M, N, dtype, eps)``:
+y = x * rsqrt(mean(x^2) + eps) * w.  dtype "float16" / "bfloat16" (or "fp16" / "bf16"), fp32 math.
 """
 
 from ..kernels.rowwise_b200 import RowConfig, check_config, make_rowwise
@@ -100,3 +103,17 @@ class RowwiseOperator(Operator):
 
     def describe(self) -> str:
         return f"{self.name}(M={self.M}, N={self.N}, {self.dtype})"
+
+
+class Softmax(RowwiseOperator):
+    op_kind = "softmax"
+
+    def __init__(self, M: int, N: int, dtype: str = "float16", name: str = "Softmax"):
+        super().__init__(M, N, dtype, name=name)
+
+
+class RMSNorm(RowwiseOperator):
+    op_kind = "rmsnorm"
+
+    def __init__(self, M: int, N: int, dtype: str = "float16", eps: float = 1e-6, name: str = "RMSNorm"):
+        super().__init__(M, N, dtype, eps, name=name)

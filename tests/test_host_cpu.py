@@ -203,3 +203,35 @@ print("ok")
     for cli in ("test_gemm_tc.py", "test_flash_attn.py", "test_rowwise.py"):
         res = subprocess.run([sys.executable, os.path.join(root, cli), "--help"], capture_output=True, text=True, cwd="/tmp")
         assert res.returncode == 0 and "--shape" in res.stdout and "--sweep" in res.stdout, res.stderr[-500:]
+
+
+def test_bench_reference_arm_line_and_config():
+    """``bench.py --impl reference`` runs without a GPU, prints one JSON line with the keys the
+    benchmark contract names, and its ``config`` is the dict the GPU arm prints for the same N."""
+    import json
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "8", "--steps", "1",
+                          "--warmup", "0"], capture_output=True, text=True, cwd=root, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    line = json.loads(res.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["n_gpus"] == 8 and line["unit"] == "TFLOPS" and line["value"] > 0
+    assert line["higher_is_better"] is True and line["scaling"] == "strong" and line["vs_baseline"] is None
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1 and line["cpu_baseline"]["sample"]
+    assert line["e2e"] == {"value": line["value"], "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    sys.path.insert(0, root)
+    import bench
+
+    for name in ("gemm_sharded", "attention_sharded", "rowwise", "gemm", "attention", "gemm_gather", "attention_gather"):
+        wl = bench.make_workload(name)
+        cfg = wl.config(8)
+        assert cfg == bench.make_workload(name).config(8) and "workload" in cfg and json.dumps(cfg)
+    assert line["config"] == bench.make_workload("gemm_sharded").config(8)
+    assert line["config"]["M"] == 65536 and line["config"]["M_per_gpu"] == 8192
+    keys = [r.key for r in bench.default_records(1, "gemm_sharded")]
+    assert {"gemm_4096x4096x4096", "gemm_8192x8192x8192", "gemm_16384x16384x16384", "fa_4x16x4096x128",
+            "fa_4x16x4096x128_causal", "fa_4x16x4096x64", "fa_4x16x4096x64_causal", "rowwise_16384x4096",
+            "attention_sharded"} <= set(keys)
+    assert [r.key for r in bench.default_records(8, "gemm_sharded")] == ["rowwise_16384x4096", "attention_sharded"]

@@ -303,3 +303,70 @@ def test_stats_argument_errors(native):
     tma = native.RowCfg(128, 2, 8, native.ROW_TMA, 2, 0)
     assert L.deca_rowwise_stats(0, 0, x.data_ptr(), None, x.data_ptr(), stats.data_ptr(), 8, 1024, eps, ctypes.byref(tma), st) == -5
     torch.cuda.synchronize()
+
+
+# ------------------------------------------------------------------ cluster mode (long rows, one pass)
+CLUSTER_CASES = [((64, 32000), dict(tpr=512, mode="cluster", unroll=2, hint=True)),
+                 ((64, 32000), dict(tpr=256, mode="cluster", unroll=4)),
+                 ((16, 128256), dict(tpr=512, mode="cluster", unroll=8, hint=True)),
+                 ((16, 128256), dict(tpr=1024, mode="cluster", unroll=4, vec=4)),
+                 ((32, 65536), dict(tpr=1024, mode="cluster", unroll=8)),
+                 ((9, 16392), dict(tpr=256, mode="cluster", unroll=2)),      # slices end inside a vector stride
+                 ((5, 1000), dict(tpr=32, mode="cluster", unroll=4)),        # short rows: most CTAs nearly idle
+                 ((3, 24), dict(tpr=32, mode="cluster", unroll=8, vec=2))]   # more CTAs than vectors
+
+
+@pytest.mark.parametrize("op", ["softmax", "rmsnorm"])
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape,cfg", CLUSTER_CASES, ids=lambda v: "x".join(map(str, v)) if isinstance(v, tuple) else ",".join(f"{k}={x}" for k, x in v.items()))
+def test_cluster_mode_matches_oracle(native, op, dtype, shape, cfg):
+    """A thread-block cluster shares a row: each CTA caches a slice in registers and the row maximum /
+    sums are combined through distributed shared memory.  Same arithmetic as the register mode: checked
+    against the oracle, and the fp32 row statistics against float64."""
+    x_bits, w_bits = make_x(*shape, dtype, seed=23)
+    w = w_bits if op == "rmsnorm" else None
+    y_bits = run_native(native, op, dtype, x_bits, w, cfg)
+    check(op, dtype, x_bits, w_bits, y_bits)
+    y2, stats = run_native_stats(native, op, dtype, x_bits, w, cfg)
+    assert np.array_equal(y2, y_bits)
+    x64 = oracle.from_bits(x_bits, dtype).astype(np.float64)
+    if op == "rmsnorm":
+        r_exact = 1.0 / np.sqrt((x64 * x64).mean(axis=1) + 1e-6)
+        assert np.all(np.abs(stats[:, 0] - r_exact) <= 5e-6 * r_exact)
+    else:
+        log2e = np.float32(1.4426950408889634)
+        ml = oracle.from_bits(x_bits, dtype).max(axis=1) * log2e
+        assert np.array_equal(stats[:, 0], ml)
+        s_exact = np.exp2(x64 * float(log2e) - ml.astype(np.float64)[:, None]).sum(axis=1)
+        assert np.all(np.abs(stats[:, 1].astype(np.float64) * s_exact - 1.0) <= 1e-5)
+
+
+def test_cluster_mode_equals_register_mode_bits(native):
+    """Where a row fits both modes the outputs are identical up to the summation order of the row
+    statistic (softmax: the same maximum, sums within rounding; in practice the same bits in > 99 %)."""
+    x_bits, w_bits = make_x(128, 8192, "float16", seed=29)
+    for op, w in (("softmax", None), ("rmsnorm", w_bits)):
+        reg = run_native(native, op, "float16", x_bits, w, dict(tpr=256, mode="reg"))
+        clu = run_native(native, op, "float16", x_bits, w, dict(tpr=256, mode="cluster", unroll=4))
+        assert np.mean(reg == clu) > 0.99
+        a, b = oracle.from_bits(reg, "float16"), oracle.from_bits(clu, "float16")
+        assert np.all(np.abs(a - b) <= ulp(a, "float16") * 1.0001)
+
+
+def test_cluster_config_rules(native):
+    L = native.lib()
+
+    def rc(M, N, *fields):
+        return L.deca_rowwise_check_config(0, 0, M, N, ctypes.byref(native.RowCfg(*fields)))
+
+    assert rc(1024, 128256, 512, 1, 8, native.ROW_CLUSTER, 8, 1) == 0
+    assert rc(1024, 128256, 512, 1, 8, native.ROW_CLUSTER, 3, 1) == -4   # clusters of 2, 4 or 8
+    assert rc(1024, 128256, 512, 2, 8, native.ROW_CLUSTER, 8, 1) == -4   # one row per cluster
+    assert rc(1024, 128256, 128, 1, 8, native.ROW_CLUSTER, 2, 1) == -4   # the slice does not fit the registers
+    assert rc(1024, 128256, 48, 1, 8, native.ROW_CLUSTER, 8, 1) == -4
+    from deca_b200.kernels.rowwise_b200 import RowConfig, check_config
+
+    check_config(RowConfig(512, 1, 8, "cluster", 8, True), "softmax", 1024, 128256, "float16")
+    with pytest.raises(AssertionError):
+        check_config(RowConfig(128, 1, 8, "cluster", 2), "softmax", 1024, 128256, "float16")
+    assert str(RowConfig(512, 1, 8, "cluster", 8, True)) == "tpr=512,rpb=1,vec=8,mode=cluster,unroll=8,hint=1"
