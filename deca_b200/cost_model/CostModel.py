@@ -248,16 +248,20 @@ def rowwise_score(cfg, arch: Arch, op: str, M: int, N: int, type_size: int = 2) 
     inst_per_elem = 8.0 if op == "softmax" else 5.0
     elems_per_clk = arch.dram_bw * 1e9 / arch.sm_nums / arch.sm_clock_hz / (2 * type_size)
     warps = ctas * cfg.threads / 32
-    issue_capacity = 4.0 * min(1.0, warps / 24.0) * 32
+    issue_capacity = 4.0 * min(1.0, warps / 16.0) * 32
     issue = min(1.0, issue_capacity / (inst_per_elem * elems_per_clk * 2.2))
 
     if cfg.mode == "tma":
         grid_eff = 1.0
-        coupling = 0.9  # per-row barrier round trips of the single persistent CTA (measured)
+        coupling = 0.72  # per-row barrier round trips of the single persistent CTA (measured 0.78 - 0.88 of the best reg config)
     else:
         grid = M // cfg.rows_per_block * (cfg.unroll if cfg.mode == "cluster" else 1)
         slots = arch.sm_nums * ctas
         grid_eff = grid / (math.ceil(grid / slots) * slots)
+        if grid >= 4 * slots:
+            # many small CTAs per SM drain unevenly anyway: the last partial wave costs a fraction of
+            # what whole-wave arithmetic says (fitted to the 4096-row shapes of the sweep)
+            grid_eff = 1.0 - 0.3 * (1.0 - grid_eff)
         coupling = 0.88 ** math.log2(cfg.rows_per_block) if cfg.threads > 128 else 1.0
 
     passes = 1.0
@@ -268,13 +272,28 @@ def rowwise_score(cfg, arch: Arch, op: str, M: int, N: int, type_size: int = 2) 
 
     nw = cfg.threads_per_row // 32
     reduce = 1.0 / (1.0 + 0.02 * math.log2(nw or 1) + (0.03 if nw > 1 else 0.0))
-    if cfg.mode == "cluster":  # a cluster barrier per reduction on top of the CTA's own
-        reduce /= 1.0 + 0.02 * math.log2(cfg.unroll)
+    if cfg.mode == "cluster":
+        # load, reduce, combine across the cluster, (exponentials, reduce, combine,) store: the phases
+        # of a row serialise on cluster barriers at two or three resident CTAs per SM; measured
+        # 3.0 - 3.8 TB/s on vocabulary rows where the two-pass mode streams at 4.2 - 5.1
+        reduce *= 0.72 / (1.0 + 0.03 * math.log2(cfg.unroll))
     covered = chunks * cfg.threads_per_row * cfg.vec * (cfg.unroll if cfg.mode == "cluster" else 1)
     tail = N / covered if cfg.mode != "twopass" else 1.0
-    lanes = 1.0 if cfg.vec * type_size >= 16 else 0.97
-    hint = 1.01 if cfg.hint else 1.0
-    return mem * phase * issue * grid_eff * coupling * reduce * (0.7 + 0.3 * tail) * lanes * hint / passes
+    lanes = 1.0 if cfg.vec * type_size >= 16 else 0.95
+    hint = 1.005 if cfg.hint else 1.0
+    # elements cached per thread (measured over the hidden-size grid, 12 configs per shape): 64 per
+    # thread (eight 16-byte chunks) are best, 32 lose 5 - 13 %, fewer more, 128 lose about 30 % (the
+    # row no longer overlaps its own loads with its reduction)
+    depth = 1.0
+    if cfg.mode in ("reg", "cluster"):
+        per_thread_elems = chunks * cfg.vec
+        if cfg.mode == "reg" and cfg.threads >= 512:
+            # one or two 512- / 1024-thread CTAs per SM: the whole SM waits in the same phase
+            # (32000 columns: 0.70 - 0.80 of the two-pass mode)
+            phase *= 0.78
+        depth = (0.8 if per_thread_elems <= 8 else 0.86 if per_thread_elems <= 16 else 0.93 if per_thread_elems <= 32
+                 else 0.97 if per_thread_elems < 56 else 1.0 if per_thread_elems <= 64 else 0.85 if per_thread_elems <= 96 else 0.7)
+    return mem * phase * issue * grid_eff * coupling * reduce * (0.7 + 0.3 * tail) * lanes * hint * depth / passes
 
 
 def rank_rowwise_configs(configs, arch: Arch, op: str, M: int, N: int, top_n: int | None = None):

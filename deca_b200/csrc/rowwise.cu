@@ -700,21 +700,27 @@ extern "C" int deca_rowwise_default_config(int op, int dtype, int64_t M, int64_t
     c.hint = 1;  // every byte is touched once: keep it out of L1 and stream the stores
     c.unroll = 1;
     c.mode = DECA_ROW_REG;
-    // about four chunks (32 elements) per thread; measured on B200 at 16384 x 4096 this (with
-    // 128-thread CTAs) reaches 95 % of the device-copy bandwidth, ahead of the bulk-copy mode
+    // about eight chunks (64 elements) per thread and CTAs of 64 threads: measured best or within 1 %
+    // of it over the hidden-size grid (1024 ... 8192 columns x 4096 ... 65536 rows); four chunks per
+    // thread lose 5 - 13 % on the widest rows, sixteen lose 30 %
     int64_t tpr = 32;
-    while (tpr < 1024 && tpr * c.vec * 4 < N) tpr *= 2;
+    while (tpr < 1024 && tpr * c.vec * 8 < N) tpr *= 2;
     c.threads_per_row = (int)tpr;
     c.rows_per_block = 1;
     int rpb = 1;
-    while (rpb * 2 * c.threads_per_row <= 128 && M % (rpb * 2) == 0) rpb *= 2;
+    while (rpb * 2 * c.threads_per_row <= 64 && M % (rpb * 2) == 0) rpb *= 2;
     c.rows_per_block = rpb;
-    if (deca_rowwise_check_config(op, dtype, M, N, &c) != DECA_OK) {
-        // the row does not fit the register file of one CTA: stream it twice
+    // Softmax rows beyond 16 Ki elements (vocabulary rows) stream twice even where they would fit the
+    // registers of a large CTA: measured 3.96 - 4.71 TB/s against 2.76 - 3.32 for a 1024-thread register
+    // CTA at 32000 columns (one such CTA per SM hides no latency), and 4.2 - 4.6 at 128256 columns;
+    // the cluster mode measures 3.0 - 3.8 there and stays a tunable.
+    const bool long_softmax = op == DECA_SOFTMAX && N > 16384;
+    if (long_softmax || deca_rowwise_check_config(op, dtype, M, N, &c) != DECA_OK) {
+        // ... or the row does not fit the register file of one CTA
         c.mode = DECA_ROW_TWOPASS;
-        c.threads_per_row = 512;
+        c.threads_per_row = N < 65536 ? 256 : 512;
         c.rows_per_block = 1;
-        c.unroll = 4;
+        c.unroll = N < 65536 ? 4 : 2;
         while (c.unroll > 1 && (int64_t)c.threads_per_row * c.vec * c.unroll > N) c.unroll /= 2;
         while (c.threads_per_row > 32 && (int64_t)c.threads_per_row * c.vec > N) c.threads_per_row /= 2;
     }

@@ -82,9 +82,14 @@ def test_every_rowwise_solution_is_valid(arch):
                 check_config(c, op, *shape, "float16")
             top = rank_rowwise_configs(cfgs, arch, op, *shape, top_n=3)
             assert all(t in cfgs for t in top)
-    # measured on B200 at 16384 x 4096: register mode, 128 threads per row, one row per CTA
+    # measured on B200 over the hidden-size grid: register mode, 64 elements per thread, one row per CTA
     top = rank_rowwise_configs(solve_rowwise(arch, "softmax", 16384, 4096), arch, "softmax", 16384, 4096)[0]
-    assert (top.mode, top.threads_per_row, top.rows_per_block) == ("reg", 128, 1)
+    assert (top.mode, top.threads_per_row, top.rows_per_block, top.vec) == ("reg", 64, 1, 8)
+    top = rank_rowwise_configs(solve_rowwise(arch, "rmsnorm", 65536, 8192), arch, "rmsnorm", 65536, 8192)[0]
+    assert (top.mode, top.threads_per_row, top.vec) == ("reg", 128, 8)
+    # vocabulary rows: the two-pass mode ahead of the one-pass cluster mode (measured 4.2 - 5.1 against 3.0 - 3.8 TB/s)
+    ranked = rank_rowwise_configs(solve_rowwise(arch, "softmax", 4096, 128256), arch, "softmax", 4096, 128256)
+    assert ranked[0].mode == "twopass" and any(c.mode == "cluster" for c in ranked)
     # rows that cannot live in registers fall back to the two-pass mode
     assert all(c.mode == "twopass" for c in solve_rowwise(arch, "softmax", 1024, 1 << 20))
 
