@@ -47,20 +47,21 @@ FALLBACK_BF16_TFLOPS_SUSTAINED = 1400.0
 NOMINAL_HBM_GBS = 8000.0
 NOMINAL_F16_TFLOPS = 2250.0
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels,
-# from ncu captures of exactly these shapes (None: no capture of that shape).
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each record's kernel, from
+# one-launch ncu captures of exactly these shapes with the default configs (read + written).
 NCU_TRAFFIC_BYTES = {
-    # softmax fp16 X[16384, 4096]: 134.23 MB read + 83.40 MB written (part of the output is still
-    # dirty in L2 when the kernel ends)
-    "rowwise_softmax_f16_16384x4096": 217628672,
-    # GEMM 4096^3: 80.51 MB read + 6.59 MB written (C mostly still in L2)
-    "gemm_f16_4096x4096x4096": 87099392,
+    "gemm_f16_65536x8192x8192": 6246289664 + 1060927488,   # A + B + C = 2.28 GB: B streams past bands of A
+    "gemm_f16_2048x2048x2048": 16822528 + 0,               # C still in L2 when the kernel ends
+    "gemm_f16_4096x4096x4096": 80066816 + 6435584,
+    "gemm_f16_8192x8192x8192": 879593984 + 120230912,
+    "gemm_f16_16384x16384x16384": 6821973504 + 528499200,
+    "fa_fwd_f16_4x16x4096x128": 201451264 + 43802624,      # Q + K + V = 201.3 MB, O = 67.1 MB partly still in L2
+    "fa_fwd_f16_4x16x4096x128_causal": 201725952 + 48557568,
+    "fa_fwd_f16_4x16x4096x64": 100756224 + 13899520,
+    "fa_fwd_f16_4x16x4096x64_causal": 100818688 + 15640576,
+    # softmax fp16 X[16384, 4096]: 134.2 MB read + 81.4 MB written (part of the output is still dirty in L2)
+    "rowwise_softmax_f16_16384x4096": 134236928 + 81434368,
 }
-# Traffic of shapes captured at another batch or row count, where it grows in proportion:
-# attention B2 H16 S4096 D128: 100.82 MB + 11.12 MB (non-causal), 100.82 MB + 15.53 MB (causal); x 2 for B = 4
-NCU_TRAFFIC_BYTES["fa_fwd_f16_4x16x4096x128"] = 2 * (100822016 + 11123712)
-NCU_TRAFFIC_BYTES["fa_fwd_f16_4x16x4096x128_causal"] = 2 * (100815104 + 15534080)
-
 
 def measured_peaks():
     try:

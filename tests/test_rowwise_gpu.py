@@ -336,7 +336,10 @@ def test_cluster_mode_matches_oracle(native, op, dtype, shape, cfg):
         # also see the rare element whose intermediate rounding flips with the last bit of r)
         _, ref32 = oracle.rmsnorm(x_bits, w_bits, 1e-6, dtype, want_f32=True)
         err = np.abs(oracle.from_bits(y_bits, dtype) - ref32)
-        assert np.all(err <= rowwise_allowed(ref32, dtype, "rmsnorm"))
+        # three 16-bit ulps here instead of two: over millions of elements of long rows the intermediate
+        # rounding flips where x * r lies one binade above the output (2 |w| output ulps) and the final
+        # rounding adds up to one more; the exact check below is the binding one
+        assert np.all(err <= 1e-3 * np.abs(ref32) + 3.0 * ulp(ref32, dtype))
         r_exact = 1.0 / np.sqrt((x64 * x64).mean(axis=1) + 1e-6)
         r = stats[:, 0]
         assert np.all(np.abs(r - r_exact) <= 5e-6 * r_exact)
