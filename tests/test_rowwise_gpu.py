@@ -277,20 +277,26 @@ def test_softmax_fp32_statistics_and_rounding(native, dtype, cfg):
         x_bits, _ = make_x(*shape, dtype, seed=17, scale=scale)
         y_bits, stats = run_native_stats(native, "softmax", dtype, x_bits, None, cfg)
         assert np.array_equal(y_bits, run_native(native, "softmax", dtype, x_bits, None, cfg))
-        x32 = oracle.from_bits(x_bits, dtype)
-        log2e = np.float32(1.4426950408889634)
-        ml = x32.max(axis=1) * log2e
-        assert np.array_equal(stats[:, 0], ml), "row max * log2(e) is an exact fp32 product"
-        x64 = x32.astype(np.float64)
-        s_exact = np.exp2(x64 * float(log2e) - ml.astype(np.float64)[:, None]).sum(axis=1)
-        inv = stats[:, 1].astype(np.float64)
-        assert np.all(np.abs(inv * s_exact - 1.0) <= 1e-5), f"1/sum off by {np.abs(inv * s_exact - 1).max():.2e}"
-        arg = (x32 * log2e - ml[:, None]).astype(np.float64)  # fma in the kernel: within half an fp32 ulp of this
-        y_exact = np.exp2(arg) * inv[:, None]
-        got = oracle.from_bits(y_bits, dtype).astype(np.float64)
-        # half a 16-bit ulp of rounding + the fp32 error of the exponential and of its argument
-        slack = 0.5 * ulp(y_exact, dtype) * 1.0001 + 1e-5 * y_exact + (3e-8 if dtype == "float16" else 0.0)
-        assert np.all(np.abs(got - y_exact) <= slack), f"max excess x{(np.abs(got - y_exact) / slack).max():.3f}"
+        assert_softmax_follows_stats(x_bits, y_bits, stats, dtype)
+
+
+def assert_softmax_follows_stats(x_bits, y_bits, stats, dtype):
+    """Row max * log2(e) exact, 1 / sum within 1e-5 of float64, and every output the correctly rounded
+    16-bit value of exp2(x * log2 e - max * log2 e) / sum up to the fp32 accuracy of the exponential."""
+    x32 = oracle.from_bits(x_bits, dtype)
+    log2e = np.float32(1.4426950408889634)
+    ml = x32.max(axis=1) * log2e
+    assert np.array_equal(stats[:, 0], ml), "row max * log2(e) is an exact fp32 product"
+    x64 = x32.astype(np.float64)
+    s_exact = np.exp2(x64 * float(log2e) - ml.astype(np.float64)[:, None]).sum(axis=1)
+    inv = stats[:, 1].astype(np.float64)
+    assert np.all(np.abs(inv * s_exact - 1.0) <= 1e-5), f"1/sum off by {np.abs(inv * s_exact - 1).max():.2e}"
+    arg = (x32 * log2e - ml[:, None]).astype(np.float64)  # fma in the kernel: within half an fp32 ulp of this
+    y_exact = np.exp2(arg) * inv[:, None]
+    got = oracle.from_bits(y_bits, dtype).astype(np.float64)
+    # half a 16-bit ulp of rounding + the fp32 error of the exponential and of its argument
+    slack = 0.5 * ulp(y_exact, dtype) * 1.0001 + 1e-5 * y_exact + (3e-8 if dtype == "float16" else 0.0)
+    assert np.all(np.abs(got - y_exact) <= slack), f"max excess x{(np.abs(got - y_exact) / slack).max():.3f}"
 
 
 def test_stats_argument_errors(native):
@@ -346,12 +352,12 @@ def test_cluster_mode_matches_oracle(native, op, dtype, shape, cfg):
         normed = oracle.from_bits(oracle.to_bits(x32 * r[:, None].astype(np.float32), dtype), dtype)
         assert np.array_equal(y_bits, oracle.to_bits(normed * oracle.from_bits(w_bits, dtype)[None, :], dtype))
     else:
-        check(op, dtype, x_bits, w_bits, y_bits)
-        log2e = np.float32(1.4426950408889634)
-        ml = oracle.from_bits(x_bits, dtype).max(axis=1) * log2e
-        assert np.array_equal(stats[:, 0], ml)
-        s_exact = np.exp2(x64 * float(log2e) - ml.astype(np.float64)[:, None]).sum(axis=1)
-        assert np.all(np.abs(stats[:, 1].astype(np.float64) * s_exact - 1.0) <= 1e-5)
+        # against the oracle's fp32 value, and exactly from the kernel's own statistics (the oracle's
+        # rounded outputs sum 128 Ki terms sequentially in fp32, which is less accurate than the kernel)
+        _, ref32 = oracle.softmax(x_bits, dtype, want_f32=True)
+        err = np.abs(oracle.from_bits(y_bits, dtype) - ref32)
+        assert np.all(err <= rowwise_allowed(ref32, dtype) + 1e-4 * np.abs(ref32))
+        assert_softmax_follows_stats(x_bits, y_bits, stats, dtype)
 
 
 def test_cluster_mode_equals_register_mode_bits(native):
