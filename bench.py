@@ -263,6 +263,7 @@ class GemmWorkload(Workload):
         self.launches = [lambda a=a, b=b, c=c: self.main(a, b, c) for a, b, c in self.sets]
         self.baseline = [lambda a=a, b=b, c=c: torch.matmul(a, b, out=c) for a, b, c in self.sets]
         self.units = self.op.num_flops * (env.world if self.shard_m else 1)
+        self.traffic_key = f"gemm_f16_{M}x{N}x{K}"  # the shape one GPU runs
         self.kernel = f"gemm16 {self.cfg}"
         self.env = env
 
@@ -463,6 +464,7 @@ class AttentionWorkload(Workload):
         scale, causal = self.op.softmax_scale, self.causal
         self.baseline = [lambda q=q, k=k, v=v: sdpa_flash(q, k, v, causal=causal, scale=scale) for q, k, v, _ in self.sets]
         self.units = self.op.num_flops * (env.world if self.shard_bh else 1)
+        self.traffic_key = f"fa_fwd_f16_{B}x{H}x{S}x{D}{'_causal' if self.causal else ''}"  # the shape one GPU runs
         self.kernel = f"fa_fwd {'causal' if self.causal else 'non-causal'} {self.cfg}"
         self.env = env
 
