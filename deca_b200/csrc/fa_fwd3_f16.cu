@@ -15,6 +15,15 @@
 //     the epilogue of the current one.  The first product of the next item overwrites the O
 //     accumulator; it is issued after that item's first P is published, which the same warps do
 //     after their epilogue, so no extra barrier guards O.
+// The thread that issues the MMAs is the serial resource of the schedule: every mbarrier wait it
+// makes costs it 200 - 300 clocks even when the phase has long completed (its scheduler's queue
+// for shared-memory operations is kept full by the exponentials of the softmax warps beside it),
+// and its MMAs issue at the rate they execute.  So it waits for as little as it can:
+//   * a relay warp waits for the K / V tiles of a step (which land a whole step ahead) and then
+//     arrives on the same barriers as the softmax warps that publish P, so one wait per Q tile and
+//     step tells the issuer that P, V_j and K_{j+1} are all there;
+//   * a product is committed to a barrier of its own only at the end of an item: within an item
+//     the completion of the next score tile (issued behind the product) already implies it.
 // All mbarrier waits are bounded (ptx.cuh); a wait that runs out raises the CTA's abort flag and
 // every role falls through to the common teardown.
 #include <atomic>
@@ -32,7 +41,7 @@ namespace {
 
 constexpr int kBr = 128;
 constexpr int kBc = 128;
-constexpr int kThreads3 = 320;
+constexpr int kThreads3 = 352;  // TMA producer, MMA issuer, 2 x 4 softmax warps, relay
 constexpr uint32_t kOStageBytes = 8 * 4096;  // one 32 x 64 fp16 panel per softmax warp
 
 struct Fa3Args {
@@ -146,7 +155,7 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         for (int grp = 0; grp < 2; ++grp) {
             mbar_init(s_full(grp), 1);
-            mbar_init(p_full(grp), 4);
+            mbar_init(p_full(grp), 5);  // four softmax warps + the relay
             mbar_init(pv_done(grp), 1);
         }
         mbar_init(drain_bar, 1);
@@ -237,14 +246,14 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                                 kdesc + (((kd / 4) * kKVBlock + (kd % 4) * 32) >> 4), kIdescQK, kd != 0 ? 1u : 0u);
                 umma_commit(s_full(grp));
             };
-            auto issue_pv = [&](int grp, const RingPos &vp, uint32_t first) {  // O_grp (+)= P_grp V
+            auto issue_pv = [&](int grp, const RingPos &vp, uint32_t first, bool last) {  // O_grp (+)= P_grp V
                 const uint64_t vdesc = kDescV | (uint64_t)(((sKV + vp.slot * kKVBytes) & 0x3FFFFu) >> 4);
                 const uint32_t d_tmem = tO(grp);
                 const uint32_t a_tmem = tS(grp);  // P: 16 keys = 8 packed columns of the score tile
 #pragma unroll
                 for (int kk = 0; kk < kBc / 16; ++kk)
                     umma_f16_ts(d_tmem, a_tmem + kk * 8, vdesc + kk * (2048 >> 4), kIdescPV, (first | kk) != 0 ? 1u : 0u);
-                umma_commit(pv_done(grp));
+                if (last) umma_commit(pv_done(grp));  // the item's O_grp is complete
             };
             // ring positions run on from item to item: kp = K tile whose scores are issued next,
             // vp = V tile of the next product; cnt[grp] = tiles of that group handled so far
@@ -271,12 +280,7 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 advance(kp, 2);
                 for (int j = 0; j < n_b && ok; ++j) {
                     const int jn = j + 1;  // tile whose scores are issued in this step (its K is at kp)
-                    if (!mbar_wait(kv_full(vp.slot), vp.par, abort_flag) ||
-                        (jn < n_b && !mbar_wait(kv_full(kp.slot), kp.par, abort_flag))) {
-                        report_detail(g.status, 1, 4, j);
-                        ok = false;
-                        break;
-                    }
+                    // V_j and K_jn have landed once p_full completes: the relay arrives there after them
                     if (j < n_a) {
                         if (!mbar_wait(p_full(0), (cnt[0] + (uint32_t)j) & 1u, abort_flag)) {
                             report_detail(g.status, 1, 5, j);
@@ -285,7 +289,7 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         }
                         tc_fence_after_sync();
                         // the product reads P from the buffer the next score MMA overwrites
-                        issue_pv(0, vp, (uint32_t)j);
+                        issue_pv(0, vp, (uint32_t)j, jn == n_a);
                         if (jn < n_a) issue_qk(0, kp);
                     }
                     if (!mbar_wait(p_full(1), (cnt[1] + (uint32_t)j) & 1u, abort_flag)) {
@@ -294,7 +298,7 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         break;
                     }
                     tc_fence_after_sync();
-                    issue_pv(1, vp, (uint32_t)j);
+                    issue_pv(1, vp, (uint32_t)j, jn == n_b);
                     umma_commit(kv_empty(vp.slot));
                     if (jn < n_b) {
                         issue_qk(1, kp);
@@ -319,6 +323,45 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
         }
         __syncwarp();
+    } else if (warp == 10) {
+        // ------------------------------------------------------------------ relay
+        // Step j of an item needs V_j and K_{j+1}; both were requested a step or more earlier.  The
+        // relay waits for them and then arrives on p_full of both Q tiles, in the issuer's place.  An
+        // arrival must fall into the phase it is meant for, so the relay first sees the previous
+        // phase of that barrier complete (it then still runs most of a step ahead of the softmax
+        // warps' own arrivals).
+        if (lane == 0) {
+            bool ok = true;
+            RingPos kp{0, 0u}, vp{1 % stages, (uint32_t)((1 / stages) & 1)};
+            uint32_t cnt[2] = {0u, 0u};  // tiles of each group arrived for so far (all items)
+            ItemWalk walk{0, 0};
+            int pair, bh;
+            for (bool more = item_next(walk, pair, bh, true); more && ok; more = item_next(walk, pair, bh, false)) {
+                int n_a, n_b;
+                tiles_of(pair, n_a, n_b);
+                advance(kp, 2);  // K_0: the issuer waits for it itself, together with Q
+                for (int j = 0; j < n_b && ok; ++j) {
+                    const int jn = j + 1;
+                    ok = mbar_wait(kv_full(vp.slot), vp.par, abort_flag) &&
+                         (jn >= n_b || mbar_wait(kv_full(kp.slot), kp.par, abort_flag));
+                    for (int grp = (j < n_a ? 0 : 1); grp < 2 && ok; ++grp) {
+                        const uint32_t t = cnt[grp] + (uint32_t)j;
+                        if (t > 0) ok = mbar_wait(p_full(grp), (t - 1u) & 1u, abort_flag);
+                        if (ok) mbar_arrive(p_full(grp));
+                    }
+                    if (!ok) report_detail(g.status, 10, 4, j);
+                    advance(vp, 2);
+                    if (jn < n_b) advance(kp, 2);
+                }
+                cnt[0] += (uint32_t)n_a;
+                cnt[1] += (uint32_t)n_b;
+            }
+            if (!ok && *abort_flag == 0) {
+                *abort_flag = 1;
+                report_timeout(g.status, 0x414u);
+            }
+        }
+        __syncwarp();
     } else {
         // ------------------------------------------------------------------ softmax + epilogue
         const int grp = (warp - 2) >> 2;  // 0 = tile A, 1 = tile B
@@ -330,7 +373,8 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const uint32_t my_stage = sO + (uint32_t)(warp - 2) * 4096u;
         const float sl2 = g.sl2;
         bool ok = true;
-        uint32_t cnt = 0;  // tiles of this group handled so far (all items)
+        uint32_t cnt = 0;     // tiles of this group handled so far (all items)
+        uint32_t n_item = 0;  // items handled so far
         auto wait_all = [&](uint32_t bar, uint32_t parity) {
             return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag)) != 0;
         };
@@ -355,8 +399,9 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 tc_fence_after_sync();
                 const bool diag = g.causal && ((j + 1) * kBc - 1 > qt * kBr);
                 const int col0 = j * kBc;
-                // the product of the previous tile of this item completes O for a rescale
-                auto wait_prev = [&]() { return j == 0 || wait_all(pv_done(grp), (t - 1u) & 1u); };
+                // a rescale needs the product of the previous tile complete: it was issued before the
+                // score MMAs whose completion s_full has just reported, and MMAs complete in order
+                auto wait_prev = [&]() { return true; };
                 auto wait_p = [&]() { return true; };  // P reuses the score tile that was just filled
                 const bool step_ok =
                     diag ? fa_softmax_step<kBc, D, true, true>(tSg, tOg, tSg, r, col0, row_abs, sl2, j == 0, m, l, wait_p,
@@ -374,12 +419,13 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 if (lane == 0) mbar_arrive(p_full(grp));
             }
             if (!ok) break;
-            if (!wait_all(pv_done(grp), (cnt + (uint32_t)n_kv - 1u) & 1u)) {
+            if (!wait_all(pv_done(grp), n_item & 1u)) {
                 if (lane == 0 && q == 0) report_detail(g.status, 2 + grp, 9, n_kv);
                 ok = false;
                 break;
             }
             cnt += (uint32_t)n_kv;
+            ++n_item;
             // ---- epilogue: O / l -> fp16 -> this warp's staging panel -> TMA stores, 64 columns at a time
             tc_fence_after_sync();
             const float inv = 1.0f / l;
