@@ -15,10 +15,9 @@
 //     the epilogue of the current one.  The first product of the next item overwrites the O
 //     accumulator; it is issued after that item's first P is published, which the same warps do
 //     after their epilogue, so no extra barrier guards O.
-// The thread that issues the MMAs is the serial resource of the schedule: every mbarrier wait it
-// makes costs it 200 - 300 clocks even when the phase has long completed (its scheduler's queue
-// for shared-memory operations is kept full by the exponentials of the softmax warps beside it),
-// and its MMAs issue at the rate they execute.  So it waits for as little as it can:
+// The thread that issues the MMAs is the serial resource of the schedule: its MMAs issue at the
+// rate they execute, and every mbarrier wait it makes is a dependent round trip of 100 - 200
+// clocks even when the phase has long completed.  So it waits for as little as it can:
 //   * a relay warp waits for the K / V tiles of a step (which land a whole step ahead) and then
 //     arrives on the same barriers as the softmax warps that publish P, so one wait per Q tile and
 //     step tells the issuer that P, V_j and K_{j+1} are all there;
