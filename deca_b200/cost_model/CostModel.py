@@ -106,12 +106,23 @@ def gemm_tc_score(cfg, arch: Arch, M: int, N: int, K: int) -> float:
     if cfg.acc_bufs == 2 and not cfg.epi_smem:
         epi = 0.97
 
-    rate = 1.0
+    # How far A and B outgrow L2 (0 at half of L2, 1 from twice L2 on).  Kernels of that size run for
+    # milliseconds at the part's power limit, and two measured preferences come with it: the tile
+    # order matters (groups of 8 tile rows best; 16 re-read more DRAM than 8 in ncu and measure 1 - 3 %
+    # lower, 4 about 1 %, 2 and 1 up to 10 %), and the one-CTA 256 x 256 tile overtakes the CTA-pair
+    # tile on most GPUs of the pool (by 1.5 - 3 % at 6144^3 ... 16384^3: it does a little less per clock but
+    # is given a higher clock; on one box the pair tile led by 1.4 % instead), while at 4096^3, where wave
+    # tails leave power to spare, the pair tile leads by up to 1.5 %.
+    big = min(1.0, max(0.0, ((M * K + K * N) * 2 / arch.l2_bytes - 0.5) / 1.5))
+    order = {1: 0.93, 2: 0.96, 4: 0.985, 8: 1.0, 16: 0.98}.get(cfg.raster, 0.99 if cfg.raster > 8 else 0.97)
+    rate = 1.0 - big * (1.0 - order)
+    if pair:
+        rate *= 1.0 - 0.02 * big  # leaves the pair tile of the best order between the one-CTA tile's two best orders
     if pair:
         # measured: the pair kernel matches the one-CTA kernel tile for tile (512 x 256 pair tile
         # 1312-1371 TFLOPS at 4096^3, 256 x 256 pair tile 1163, narrower ones 700-850), so its
         # smaller tiles are ranked like the one-CTA tiles with the same rows and columns per CTA
-        rate = {(256, 256): 0.97, (128, 256): 0.85, (256, 128): 0.62, (128, 128): 0.52}.get((cfg.BM, cfg.BN), 0.5)
+        rate *= {(256, 256): 0.97, (128, 256): 0.85, (256, 128): 0.62, (128, 128): 0.52}.get((cfg.BM, cfg.BN), 0.5)
     return rate * wave_eff * useful * pipe * epi / (t_flop / t_mma)
 
 
@@ -207,14 +218,18 @@ def rowwise_occupancy(cfg, arch: Arch, op: str, N: int):
     if cfg.mode == "tma":
         return 1
     regs = (min(255, est_regs_per_thread(cfg, N, op)) + 7) // 8 * 8
+    if cfg.mode == "twopass":
+        # ptxas -v: 32 / 40 / 56 registers at 8 / 16 / 32 elements per iteration (the validity rule's
+        # estimate is deliberately higher)
+        regs = max(32, (24 + cfg.unroll * cfg.vec + 7) // 8 * 8)
     warps = cfg.threads // 32
     ctas = min(arch.max_registers_per_sm // (regs * cfg.threads), arch.max_resident_warps_per_sm // warps,
                arch.max_resident_blocks_per_sm)
     return max(int(ctas), 1)
 
 
-def rowwise_score(cfg, arch: Arch, op: str, M: int, N: int, type_size: int = 2) -> float:
-    """Heuristic score of a memory-bound row-wise config.
+def rowwise_terms(cfg, arch: Arch, op: str, M: int, N: int, type_size: int = 2) -> dict:
+    """The factors of ``rowwise_score`` by name (their product is the score).
 
     - memory parallelism: bytes of loads in flight per SM against Little's law (DRAM bandwidth
       per SM x ``arch.dram_latency_s``).  reg: every chunk of the row is requested up front by all
@@ -233,15 +248,24 @@ def rowwise_score(cfg, arch: Arch, op: str, M: int, N: int, type_size: int = 2) 
     ctas = rowwise_occupancy(cfg, arch, op, N)
     chunks = num_chunks(cfg, N)
     need = arch.dram_bw * 1e9 / arch.sm_nums * getattr(arch, "dram_latency_s", 1e-6)
+    grid = 0 if cfg.mode == "tma" else M // cfg.rows_per_block * (cfg.unroll if cfg.mode == "cluster" else 1)
     if cfg.mode == "tma":
         in_flight = cfg.rows_per_block * cfg.unroll * N * type_size
         phase = 1.0
     else:
+        # a grid below one wave is resident all at once: fewer CTAs per SM than the limit allows
+        ctas = max(1.0, min(float(ctas), grid / arch.sm_nums))
         cached = cfg.mode in ("reg", "cluster")  # the whole row (slice) is requested up front
         per_thread = (chunks if cached else cfg.unroll) * cfg.vec * type_size
         in_flight = ctas * cfg.threads * per_thread
         phase = 1.0 - 0.35 / ctas if cached else 1.0 - 0.1 / ctas
     mem = min(1.0, in_flight / need)
+    if cfg.mode == "twopass":
+        # streaming loop: a row of few iterations never reaches a steady state of loads in flight
+        # (32000 columns, 512 threads: 2 iterations of 4 chunks run at 0.76 of 8 iterations of 2), and
+        # more, smaller CTAs make up for fewer chunks per iteration
+        its = chunks / cfg.unroll
+        mem = mem ** 0.5 * its / (its + 0.75)
 
     # instruction issue: elements per clock per SM needed at full bandwidth vs what the resident
     # warps can issue (4 schedulers; one CTA's phases serialise on its barriers)
@@ -254,10 +278,14 @@ def rowwise_score(cfg, arch: Arch, op: str, M: int, N: int, type_size: int = 2) 
     if cfg.mode == "tma":
         grid_eff = 1.0
         coupling = 0.72  # per-row barrier round trips of the single persistent CTA (measured 0.78 - 0.88 of the best reg config)
+        # a persistent CTA starts later (barriers, tensor maps, the first bulk copy's round trip): about
+        # a microsecond more than a register-mode launch, which shows on problems that stream for only
+        # a few microseconds (4096 x 2048: 0.91 of the best register config)
+        t_stream = 2.0 * M * N * type_size / (arch.dram_bw * 1e9) + 3e-6
+        coupling *= t_stream / (t_stream + 1e-6)
     else:
-        grid = M // cfg.rows_per_block * (cfg.unroll if cfg.mode == "cluster" else 1)
-        slots = arch.sm_nums * ctas
-        grid_eff = grid / (math.ceil(grid / slots) * slots)
+        slots = arch.sm_nums * rowwise_occupancy(cfg, arch, op, N)
+        grid_eff = 1.0 if grid <= slots else grid / (math.ceil(grid / slots) * slots)
         if grid >= 4 * slots:
             # many small CTAs per SM drain unevenly anyway: the last partial wave costs a fraction of
             # what whole-wave arithmetic says (fitted to the 4096-row shapes of the sweep)
@@ -267,11 +295,13 @@ def rowwise_score(cfg, arch: Arch, op: str, M: int, N: int, type_size: int = 2) 
     passes = 1.0
     if cfg.mode == "twopass":
         footprint = arch.sm_nums * ctas * cfg.rows_per_block * N * type_size
-        hit = min(1.0, 0.6 * arch.l2_bytes / footprint)
+        hit = min(1.0, 0.6 * arch.l2_bytes / footprint) ** 2  # the rows in flight thrash L2 quickly once they outgrow it
         passes = 1.0 + 0.5 * (hit * arch.dram_bw / arch.l2_bw + (1.0 - hit))
 
     nw = cfg.threads_per_row // 32
     reduce = 1.0 / (1.0 + 0.02 * math.log2(nw or 1) + (0.03 if nw > 1 else 0.0))
+    if cfg.mode == "twopass" and cfg.threads_per_row < 128:
+        reduce *= 0.88  # a warp or two streaming a whole vocabulary row: measured 0.76 - 0.9 of 256 threads
     if cfg.mode == "cluster":
         # load, reduce, combine across the cluster, (exponentials, reduce, combine,) store: the phases
         # of a row serialise on cluster barriers at two or three resident CTAs per SM; measured
@@ -280,7 +310,18 @@ def rowwise_score(cfg, arch: Arch, op: str, M: int, N: int, type_size: int = 2) 
     covered = chunks * cfg.threads_per_row * cfg.vec * (cfg.unroll if cfg.mode == "cluster" else 1)
     tail = N / covered if cfg.mode != "twopass" else 1.0
     lanes = 1.0 if cfg.vec * type_size >= 16 else 0.95
-    hint = 1.005 if cfg.hint else 1.0
+    # no-allocate loads and streaming stores: a hair better on problems that stream through L2, 2 - 12 %
+    # worse on problems that fit in it
+    # (16384 x 1024: 0.88; a tuning run times the same buffers over and over).  The two-pass mode gains
+    # most: its second pass and its stores stream past the rows still to be re-read (+3 ... +11 %)
+    if not cfg.hint:
+        hint = 1.0
+    elif cfg.mode == "twopass":
+        hint = 1.05
+    elif 2.0 * M * N * type_size <= arch.l2_bytes:
+        hint = 0.92
+    else:
+        hint = 1.005
     # elements cached per thread (measured over the hidden-size grid, 12 configs per shape): 64 per
     # thread (eight 16-byte chunks) are best, 32 lose 5 - 13 %, fewer more, 128 lose about 30 % (the
     # row no longer overlaps its own loads with its reduction)
@@ -293,7 +334,19 @@ def rowwise_score(cfg, arch: Arch, op: str, M: int, N: int, type_size: int = 2) 
             phase *= 0.78
         depth = (0.8 if per_thread_elems <= 8 else 0.86 if per_thread_elems <= 16 else 0.93 if per_thread_elems <= 32
                  else 0.97 if per_thread_elems < 56 else 1.0 if per_thread_elems <= 64 else 0.85 if per_thread_elems <= 96 else 0.7)
-    return mem * phase * issue * grid_eff * coupling * reduce * (0.7 + 0.3 * tail) * lanes * hint * depth / passes
+    # a CTA costs the SM a fixed slice of time to start and retire, which shows when it moves only a
+    # couple of kilobytes (16384 x 1024: CTAs of two or four 2 KB rows are 7.7 % faster than of one)
+    small = 1.0
+    if cfg.mode in ("reg", "twopass") and 2.0 * M * N * type_size <= arch.l2_bytes:  # seen on L2-resident problems only
+        cta_bytes = cfg.rows_per_block * N * type_size
+        small = cta_bytes / (cta_bytes + 320.0)
+    return {"small": small, "mem": mem, "phase": phase, "issue": issue, "grid": grid_eff, "coupling": coupling, "reduce": reduce,
+            "tail": 0.7 + 0.3 * tail, "lanes": lanes, "hint": hint, "depth": depth, "passes": 1.0 / passes}
+
+
+def rowwise_score(cfg, arch: Arch, op: str, M: int, N: int, type_size: int = 2) -> float:
+    """Heuristic score of a memory-bound row-wise config: the product of ``rowwise_terms``."""
+    return math.prod(rowwise_terms(cfg, arch, op, M, N, type_size).values())
 
 
 def rank_rowwise_configs(configs, arch: Arch, op: str, M: int, N: int, top_n: int | None = None):
