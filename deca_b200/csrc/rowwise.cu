@@ -713,14 +713,17 @@ extern "C" int deca_rowwise_default_config(int op, int dtype, int64_t M, int64_t
     // Softmax rows beyond 16 Ki elements (vocabulary rows) stream twice even where they would fit the
     // registers of a large CTA: measured 3.96 - 4.71 TB/s against 2.76 - 3.32 for a 1024-thread register
     // CTA at 32000 columns (one such CTA per SM hides no latency), and 4.2 - 4.6 at 128256 columns;
-    // the cluster mode measures 3.0 - 3.8 there and stays a tunable.
+    // the cluster mode measures 3.0 - 3.8 there and stays a tunable.  Within the two-pass mode: 256 threads
+    // with two chunks per iteration at 32000 columns (4.9 - 5.2 TB/s on 4096 - 8192 rows; four chunks per
+    // iteration leave the row too few iterations: 4.6 - 4.7), 512 threads with four chunks at 128256 columns
+    // (4.7; two chunks 4.6, 256 threads 4.3: more rows in flight than L2 holds for the second pass).
     const bool long_softmax = op == DECA_SOFTMAX && N > 16384;
     if (long_softmax || deca_rowwise_check_config(op, dtype, M, N, &c) != DECA_OK) {
         // ... or the row does not fit the register file of one CTA
         c.mode = DECA_ROW_TWOPASS;
         c.threads_per_row = N < 65536 ? 256 : 512;
         c.rows_per_block = 1;
-        c.unroll = N < 65536 ? 4 : 2;
+        c.unroll = N < 65536 ? 2 : 4;
         while (c.unroll > 1 && (int64_t)c.threads_per_row * c.vec * c.unroll > N) c.unroll /= 2;
         while (c.threads_per_row > 32 && (int64_t)c.threads_per_row * c.vec > N) c.threads_per_row /= 2;
     }
