@@ -30,8 +30,13 @@ def test_every_gemm_solution_is_valid_and_ranked(arch):
         d = default_config(*shape)
         assert d in cfgs
     # large squares: the model's favourite is the tile shape measured best on B200
-    best = rank_gemm_configs(solve_gemm_tc(arch, 8192, 8192, 8192), arch, 8192, 8192, 8192)[0]
-    assert (best.BM, best.BN) == (256, 256)
+    top3 = rank_gemm_configs(solve_gemm_tc(arch, 8192, 8192, 8192), arch, 8192, 8192, 8192)[:3]
+    assert all((c.BM, c.BN) == (256, 256) for c in top3)
+    # ... in groups of 8 tile rows, the one-CTA tile first and the CTA-pair tile among the first three
+    # (either leads by 1 - 3 % depending on the GPU once the kernel runs at the power limit)
+    assert (top3[0].cta_group, top3[0].raster) == (1, 8) and any(c.cta_group == 2 and c.raster == 8 for c in top3)
+    # at 4096^3, where wave tails leave power to spare, the pair tile leads
+    assert rank_gemm_configs(solve_gemm_tc(arch, 4096, 4096, 4096), arch, 4096, 4096, 4096)[0].cta_group == 2
     # fp16-accumulate call sites get the one-CTA, whole-tile part of the same tile space with fp16 accumulators
     from dataclasses import replace
 
@@ -90,6 +95,15 @@ def test_every_rowwise_solution_is_valid(arch):
     # vocabulary rows: the two-pass mode ahead of the one-pass cluster mode (measured 4.2 - 5.1 against 3.0 - 3.8 TB/s)
     ranked = rank_rowwise_configs(solve_rowwise(arch, "softmax", 4096, 128256), arch, "softmax", 4096, 128256)
     assert ranked[0].mode == "twopass" and any(c.mode == "cluster" for c in ranked)
+    assert (ranked[0].threads_per_row, ranked[0].hint) == (512, True)  # measured 4.7 TB/s; 256 threads 4.3
+    # 32000 columns: 256 threads with two chunks per iteration (measured best) among the first three
+    top3 = rank_rowwise_configs(solve_rowwise(arch, "softmax", 8192, 32000), arch, "softmax", 8192, 32000)[:3]
+    assert any((c.mode, c.threads_per_row, c.unroll, c.hint) == ("twopass", 256, 2, True) for c in top3)
+    # problems that fit in L2: no cache hints, and not one tiny CTA per 2 KB row
+    top = rank_rowwise_configs(solve_rowwise(arch, "softmax", 16384, 1024), arch, "softmax", 16384, 1024)[:3]
+    assert not top[0].hint and any(c.rows_per_block > 1 for c in top)
+    # the persistent bulk-copy mode does not lead on problems that stream for a few microseconds
+    assert rank_rowwise_configs(solve_rowwise(arch, "softmax", 4096, 2048), arch, "softmax", 4096, 2048)[0].mode == "reg"
     # rows that cannot live in registers fall back to the two-pass mode
     assert all(c.mode == "twopass" for c in solve_rowwise(arch, "softmax", 1024, 1 << 20))
 
