@@ -82,11 +82,51 @@ __device__ __forceinline__ float fa_exp_tile(uint32_t tS, uint32_t p_base, int r
     return (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
 }
 
+// 2^x for two scores on the FMA pipe instead of the exp2 unit (x = s * sl2 - ms):
+//   t = sat(x / 256 + 126 / 256) clamps to x' = 256 t - 126 in [-126, 130) (one saturating fma per
+//   score: what lies below 2^-126 counts as 2^-126), r = x' + 1.5 * 2^23 rounds x' to the nearest
+//   integer j in r's low mantissa bits, a degree-3 polynomial (relative error 7.6e-5, a sixth of
+//   an fp16 ulp) gives 2^(x' - j) on [-0.5, 0.5], and one integer multiply-add puts j into the
+//   exponent (r's bits times 2^23 is j * 2^23 modulo 2^32).  The additions and the polynomial
+//   run as packed pairs.
+struct FaPolyConst {
+    float sl2_256, off;  // sl2 / 256, 126 / 256 - ms / 256
+};
+__device__ __forceinline__ void fa_exp2_poly_pair(float s0, float s1, const FaPolyConst &k, float &p0, float &p1) {
+    float t0, t1;
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(t0) : "f"(s0), "f"(k.sl2_256), "f"(k.off));
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(t1) : "f"(s1), "f"(k.sl2_256), "f"(k.off));
+    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+    const uint64_t x = f32x2_fma(f32x2_pack(t0, t1), f32x2_pack(256.0f, 256.0f), f32x2_pack(-126.0f, -126.0f));
+    const uint64_t r = f32x2_add(x, f32x2_pack(kMagic, kMagic));
+    const uint64_t j = f32x2_add(r, f32x2_pack(-kMagic, -kMagic));
+    const uint64_t f = f32x2_fma(j, f32x2_pack(-1.0f, -1.0f), x);
+    uint64_t q = f32x2_fma(f32x2_pack(0.05520550534f, 0.05520550534f), f, f32x2_pack(0.24261397123f, 0.24261397123f));
+    q = f32x2_fma(q, f, f32x2_pack(0.69325476885f, 0.69325476885f));
+    q = f32x2_fma(q, f, f32x2_pack(0.99992769957f, 0.99992769957f));
+    uint32_t q0, q1, r0, r1;
+    f32x2_unpack_bits(q, q0, q1);
+    f32x2_unpack_bits(r, r0, r1);
+    uint32_t e0, e1;
+    asm("mad.lo.s32 %0, %1, 8388608, %2;" : "=r"(e0) : "r"(r0), "r"(q0));
+    asm("mad.lo.s32 %0, %1, 8388608, %2;" : "=r"(e1) : "r"(r1), "r"(q1));
+    p0 = __uint_as_float(e0), p1 = __uint_as_float(e1);
+}
+
+// Share of the exponentials of an unmasked tile that is taken on the FMA pipe: every EVERY-th pair
+// of scores (0: none).  At D = 64 the exp2 unit alone bounds the kernel (half the tensor work per
+// exponential) and a share on the FMA pipe pays: 682 -> 728 ... 747 TFLOPS back to back and 700 -> 798
+// in isolated launches with every fourth pair (every fifth or eighth measure the same, every third
+// 708, every second 684).  At D = 128, where the step is a dependency chain and the pass only a part
+// of it, the longer instruction stream costs what the unit gains (1 147 -> 1 143, 1 282 -> 1 258).
+template <int D>
+constexpr int kFaPolyEveryFor = D == 64 ? 4 : 0;
+
 // 32 scores of one row (keys cb0 .. cb0 + 31): adds the exponentials 2^(s * sl2 - ms) of the
 // (masked) scores to the packed sums and packs them to fp16, keys (2i, 2i + 1) in pk[i].
-template <bool MASKED>
+template <bool MASKED, int EVERY>
 __device__ __forceinline__ void fa_exp_chunk32(const uint32_t (&v)[32], int cb0, int row_abs, uint64_t sl2x2,
-                                               uint64_t nmsx2, uint64_t (&sum2)[2], uint32_t *pk) {
+                                               uint64_t nmsx2, const FaPolyConst &pc, uint64_t (&sum2)[2], uint32_t *pk) {
     using P16 = Pack16<DECA_F16>;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -95,9 +135,14 @@ __device__ __forceinline__ void fa_exp_chunk32(const uint32_t (&v)[32], int cb0,
             if (cb0 + 2 * i > row_abs) s0 = kNegInf;
             if (cb0 + 2 * i + 1 > row_abs) s1 = kNegInf;
         }
-        float x0, x1;
-        f32x2_unpack(f32x2_fma(f32x2_pack(s0, s1), sl2x2, nmsx2), x0, x1);
-        const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+        float p0, p1;
+        if (!MASKED && EVERY > 0 && i % (EVERY > 0 ? EVERY : 1) == (EVERY > 0 ? EVERY : 1) - 1) {
+            fa_exp2_poly_pair(s0, s1, pc, p0, p1);
+        } else {
+            float x0, x1;
+            f32x2_unpack(f32x2_fma(f32x2_pack(s0, s1), sl2x2, nmsx2), x0, x1);
+            p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+        }
         sum2[i & 1] = f32x2_add(sum2[i & 1], f32x2_pack(p0, p1));
         pk[i] = P16::pack(p0, p1);
     }
@@ -108,11 +153,12 @@ __device__ __forceinline__ void fa_exp_chunk32(const uint32_t (&v)[32], int cb0,
 // a raised max still needs; the caller stores them once the warp has voted that no row grew by
 // more than the threshold.  No maximum is tracked: the caller tests the returned row sum instead.
 // The tensor-memory load of the next 32 columns is in flight while the current 32 are processed.
-template <int BC, bool MASKED>
+template <int BC, bool MASKED, int EVERY>
 __device__ __forceinline__ float fa_exp_tile_hold(uint32_t tS, int col0, int row_abs, float sl2, float ms,
                                                   uint32_t (&pk)[BC / 2]) {
     constexpr int kChunks = BC / 32;
     const uint64_t sl2x2 = f32x2_pack(sl2, sl2), nmsx2 = f32x2_pack(-ms, -ms);
+    const FaPolyConst pc = {sl2 * (1.0f / 256.0f), 126.0f / 256.0f - ms * (1.0f / 256.0f)};
     uint64_t sum2[2] = {0ull, 0ull};
     uint32_t v[2][32];
     tmem_ld_32x32b_x32(tS, v[0]);
@@ -121,7 +167,7 @@ __device__ __forceinline__ float fa_exp_tile_hold(uint32_t tS, int col0, int row
     for (int c = 0; c < kChunks; ++c) {
         if (c + 1 < kChunks) tmem_ld_32x32b_x32(tS + (c + 1) * 32, v[(c + 1) & 1]);
         // chunk c = keys 32c ..: half h = c / 2 of the tile, words (c % 2) * 16 .. of that half
-        fa_exp_chunk32<MASKED>(v[c & 1], col0 + c * 32, row_abs, sl2x2, nmsx2, sum2,
+        fa_exp_chunk32<MASKED, EVERY>(v[c & 1], col0 + c * 32, row_abs, sl2x2, nmsx2, pc, sum2,
                                &pk[(c / 2) * 32 + (c % 2) * 16]);
         if (c + 1 < kChunks) tmem_ld_wait_regs(v[(c + 1) & 1]);
     }
@@ -194,7 +240,7 @@ __device__ __forceinline__ bool fa_softmax_step(uint32_t tS, uint32_t tO, uint32
         // (no score grew by more than the threshold) without a max over the scores; a larger sum
         // sends the warp down the slow path, where the exact maximum is taken and m raised.
         uint32_t pk[BC / 2];
-        lsum = fa_exp_tile_hold<BC, MASKED>(tS, col0, row_abs, sl2, m * sl2, pk);
+        lsum = fa_exp_tile_hold<BC, MASKED, kFaPolyEveryFor<D>>(tS, col0, row_abs, sl2, m * sl2, pk);
         const bool slow = __any_sync(0xFFFFFFFFu, !(lsum <= kFaSumLimit)) != 0;
         if (!slow) {
 #pragma unroll
