@@ -283,6 +283,22 @@ class GemmWorkload(Workload):
         self.e2e_rows = max(256, self.M // 16)  # 16 chunks: the last chunk's kernel and copy-out are the pipeline's tail
         self.e2e_op = GEMMTC(self.e2e_rows, self.N, self.K)
         self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        # More than one rank: every rank needs all of B, but over the host link each uploads only its
+        # 1 / world of B's rows; the ranks then all-gather B over NVLink.  (Eight ranks uploading all of B
+        # each doubled the bytes through a host that moves 135 - 146 GB/s in total.)
+        world = self.env.world
+        self.b_rows = self.K // world if world > 1 and self.shard_m and self.K % world == 0 else 0
+        if self.b_rows:
+            self.b_part = torch.empty(self.b_rows, self.N, dtype=b.dtype, device=b.device)
+            # once, outside every timed region: the gathered B is the B every rank generated
+            r = self.env.rank
+            want = b.clone()
+            self.b_part.copy_(self.host[1][r * self.b_rows : (r + 1) * self.b_rows])
+            b.zero_()
+            self.env.dist.all_gather_into_tensor(b, self.b_part)
+            torch.cuda.synchronize()
+            if not torch.equal(b, want):
+                raise RuntimeError("B gathered from the ranks' row slices differs from the generated B")
 
     def step_e2e(self):
         import torch
@@ -295,8 +311,15 @@ class GemmWorkload(Workload):
         s_in.wait_stream(main)
         s_out.wait_stream(main)
         with torch.cuda.stream(s_in):
-            b.copy_(hb, non_blocking=True)
-        h2d, d2h = hb.numel() * 2, 0
+            if self.b_rows:
+                r = self.env.rank
+                self.b_part.copy_(hb[r * self.b_rows : (r + 1) * self.b_rows], non_blocking=True)
+                self.env.dist.all_gather_into_tensor(b, self.b_part)
+                h2d = self.b_part.numel() * 2
+            else:
+                b.copy_(hb, non_blocking=True)
+                h2d = hb.numel() * 2
+        d2h = 0
         for r0 in range(0, self.M, self.e2e_rows):
             sl = slice(r0, r0 + self.e2e_rows)
             with torch.cuda.stream(s_in):
